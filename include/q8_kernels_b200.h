@@ -1,0 +1,161 @@
+/*
+ * q8_kernels_b200 -- C ABI of the B200 (sm_100a) 8-bit DiT inference kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t), launches asynchronously on that
+ * stream, allocates nothing and never synchronises.  The return value is 0 on
+ * success or a negative Q8K_ERR_* code; q8k_error_string() explains it and
+ * q8k_last_error_detail() gives the message of the last failing call on the
+ * calling thread.
+ *
+ * Each function names the entry point of the reference extension modules
+ * (q8_kernels_cuda.{quantizer,ops,gemm,flash_attention}._C) it stands in for,
+ * by the reference's file path and line.
+ */
+#ifndef Q8_KERNELS_B200_H
+#define Q8_KERNELS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define Q8K_API __attribute__((visibility("default")))
+#else
+#define Q8K_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- return codes ------------------------------------------------------- */
+#define Q8K_OK                 0
+#define Q8K_ERR_INVALID_ARG   -1   /* null pointer, bad size, bad alignment      */
+#define Q8K_ERR_UNSUPPORTED   -2   /* dtype / shape combination not implemented  */
+#define Q8K_ERR_WORKSPACE     -3   /* caller-provided scratch too small          */
+#define Q8K_ERR_CUDA          -4   /* a CUDA runtime / driver call failed        */
+#define Q8K_ERR_TOO_LARGE     -5   /* problem exceeds a fixed built-in capacity  */
+
+/* ---- element types ------------------------------------------------------ */
+#define Q8K_DT_F32   0
+#define Q8K_DT_F16   1
+#define Q8K_DT_BF16  2
+#define Q8K_DT_E4M3  3   /* float8_e4m3fn */
+#define Q8K_DT_I8    4
+
+/* ---- device status word --------------------------------------------------
+ * The tensor-core kernels (GEMM, attention) bound every mbarrier wait.  When a
+ * wait gives up the kernel records  Q8K_STATUS_TIMEOUT | (site << 8)  in the
+ * int32 the caller passed as `dev_status` (may be NULL), drains and exits; the
+ * CUDA context stays usable.  The word is only ever written on failure, so one
+ * zero-initialised int32 per device can be shared by all calls.              */
+#define Q8K_STATUS_TIMEOUT  0x1
+
+Q8K_API int         q8k_version(void);
+Q8K_API const char* q8k_error_string(int code);
+Q8K_API const char* q8k_last_error_detail(void);
+
+/* Per-row absmax quantizer.  x [rows, dim] (row stride x_row_stride elements)
+ * -> q [rows, dim] int8 (round half away from zero) or e4m3 (RNE, overflow ->
+ * NaN) and scales[rows] = absmax / QMAX.  An all-zero row gives q = 0,
+ * scale = 0.  dim must be a multiple of 16.
+ * Replaces tokenwise_quant: csrc/quantizer/tokenwise_quant.cpp:74-111,
+ * csrc/quantizer/tokenwise_quant_cuda.cu:91-149.                              */
+Q8K_API int q8k_tokenwise_quant(const void* x, int x_dtype, void* q, int q_dtype, float* scales,
+                        int64_t rows, int dim, int64_t x_row_stride, void* stream);
+
+/* Fast Walsh-Hadamard transform of every row (zero-padded to the next power of
+ * two, fp32 butterflies in ascending stride order), out = cast(y * scale).
+ * x bf16|e4m3, out bf16|e4m3; dim a multiple of 8, at most 16384.
+ * Replaces fast_hadamard_transform:
+ * csrc/fast_hadamard/fast_hadamard_transform.cpp:70-121,
+ * csrc/fast_hadamard/fast_hadamard_transform_cuda.cu:42-111.                  */
+Q8K_API int q8k_fast_hadamard_transform(const void* x, int x_dtype, void* out, int out_dtype,
+                                int64_t rows, int dim, int64_t x_row_stride, float scale,
+                                void* stream);
+
+/* Fused producer for the linear layers: Hadamard (rounded to the input dtype,
+ * as the unfused chain does) followed by the per-row quantizer, one pass over
+ * x.  Bit-identical to q8k_fast_hadamard_transform + q8k_tokenwise_quant.
+ * Replaces the chain in q8_kernels/functional/linear.py:30-31,143-145.        */
+Q8K_API int q8k_hadamard_quant(const void* x, int x_dtype, void* q, int q_dtype, float* scales,
+                       int64_t rows, int dim, int64_t x_row_stride, float scale, void* stream);
+
+/* RMS norm without eps: r = rsqrt(mean(x^2)), out = (x*r)*w (w fp32 or NULL),
+ * rrms[rows] = r (may be NULL).  x, out bf16|e4m3; dim a multiple of 16.
+ * Replaces rms_norm: csrc/ops/rms_norm.cpp:103-154, rms_norm_cuda.cu:100-171. */
+Q8K_API int q8k_rms_norm(const void* x, int x_dtype, const float* weights, void* out, int out_dtype,
+                 float* rrms, int64_t rows, int dim, void* stream);
+
+/* Interleaved-pair rotary embedding with per-element fp32 cos/sin tables that
+ * have x's shape; `freq_rows` > 0 makes the tables repeat every freq_rows rows
+ * (one table shared by all batch entries), 0 means one table row per x row.
+ * Replaces rope: csrc/ops/rope.cpp:96-146, rope_cuda.cu:67-106.               */
+Q8K_API int q8k_rope(const void* x, int x_dtype, const float* cos_freqs, const float* sin_freqs,
+             void* out, int out_dtype, int64_t rows, int dim, int64_t freq_rows, void* stream);
+
+/* out_e4m3 = cast(float(x_e4m3) * (y + scale_add) + z); row r of x uses row
+ * r / y_every of y and r / z_every of z.  (y,z) dtypes: (f32,f32), (f32,e4m3),
+ * (bf16,bf16).  Replaces fma_8bit: csrc/ops/fma.cpp:72-118, fma_cuda.cu:60-98. */
+Q8K_API int q8k_fma_8bit(const void* x, const void* y, int y_dtype, const void* z, int z_dtype, void* out,
+                 int64_t rows, int dim, int64_t y_every, int64_t z_every, float scale_add,
+                 void* stream);
+
+/* tanh-GELU, x/out bf16|e4m3.  Replaces gelu_forward:
+ * csrc/ops/gelu_act.cpp:132-172, gelu_forward_cuda.cu:72-100.                 */
+Q8K_API int q8k_gelu_forward(const void* x, int x_dtype, void* out, int out_dtype, int64_t rows, int dim,
+                     void* stream);
+
+/* 8-bit GEMM  C[b] = act((A[b] . B[b]^T) * (sa[m]*sb[n]) + bias[n]).
+ * A [bs_a, M, K], B [bs_b, N, K] K-contiguous int8 (q8k_q8_mm) or e4m3
+ * (q8k_fp8_mm); bs_a == bs_b or one of them 1; sa [bs_a, M], sb [bs_b, N],
+ * bias [N] fp32 or NULL; C [max(bs_a,bs_b), M, N] bf16 (RNE) or e4m3
+ * (saturating).  N % 16 == 0, K % 16 == 0, all pointers 16-byte aligned.
+ * Replaces q8_mm / q8_mm_bias / fp8_mm / fp8_mm_bias:
+ * csrc/gemm/q8_gemm_api.cpp:40-291 and the run_* launchers declared at :27-35. */
+Q8K_API int q8k_q8_mm(const void* a, const void* b, const float* bias, const float* a_scales,
+              const float* b_scales, void* out, int out_dtype, int bs_a, int bs_b,
+              int M, int N, int K, int fuse_gelu, int* dev_status, void* stream);
+Q8K_API int q8k_fp8_mm(const void* a, const void* b, const float* bias, const float* a_scales,
+               const float* b_scales, void* out, int out_dtype, int bs_a, int bs_b,
+               int M, int N, int K, int fuse_gelu, int* dev_status, void* stream);
+
+/* FP8 flash-attention forward, head dim 64.  q [B,H,M,64], k [B,H,N,64],
+ * vt [B,H,64,ceil16(N)] e4m3 contiguous; out [B,H,M,64] e4m3 (saturating) or
+ * bf16; key_lens int32 [B] valid keys per batch entry or NULL.  KV blocks are
+ * visited last to first with an exact running max.
+ * Replaces flash_attention: csrc/flash_attention/flash_attention.cpp:18-48 and
+ * the launchers declared at :9-16.                                            */
+Q8K_API int q8k_flash_attention(const void* q, const void* k, const void* vt, void* out, int out_dtype,
+                        int B, int H, int M, int N, float softmax_scale, const int* key_lens,
+                        int* dev_status, void* stream);
+
+/* Pre-pass of the attention call: from bf16 q,k,v given as strided [B,S,H,64]
+ * views (strides in elements, last dim contiguous) produce q8,k8 [B,H,S,64]
+ * e4m3 (Hadamard-rotated times qk_scale when apply_hadamard, else plain cast)
+ * and vt [B,H,64,ceil16(S_kv)] e4m3 (transposed, zero padded).
+ * Replaces the torch glue in q8_kernels/functional/flash_attention.py:30-60.  */
+Q8K_API int q8k_attention_prep(const void* q, const void* k, const void* v,
+                       void* q8, void* k8, void* vt8,
+                       int B, int H, int S_q, int S_kv,
+                       int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
+                       int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
+                       int64_t v_stride_b, int64_t v_stride_s, int64_t v_stride_h,
+                       int apply_hadamard, float qk_scale, void* stream);
+
+/* Whole activation side of Q8Linear / FP8Linear in one call: fused Hadamard +
+ * per-token quantizer into caller-provided scratch, then the GEMM.
+ * x bf16 [M,K]; w int8|e4m3 [N,K] with w_scales [N]; workspace must hold
+ * q8k_linear_workspace_bytes(M,K) bytes, 256-byte aligned.
+ * Replaces Q8LinearFunc.forward / FP8LinearFunc.forward:
+ * q8_kernels/functional/linear.py:24-42,138-159.                              */
+Q8K_API size_t q8k_linear_workspace_bytes(int M, int K);
+Q8K_API int q8k_linear(const void* x, int x_dtype, const void* w, int w_dtype, const float* w_scales,
+               const float* bias, void* out, int out_dtype, int M, int N, int K,
+               int use_hadamard, int fuse_gelu, void* workspace, size_t workspace_bytes,
+               int* dev_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q8_KERNELS_B200_H */

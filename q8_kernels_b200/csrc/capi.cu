@@ -1,0 +1,73 @@
+// C-ABI plumbing shared by all entry points: version, error strings, the
+// per-thread error detail, and the fused linear chain that strings the producer
+// kernel and the GEMM together over caller-provided scratch.
+
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace q8k {
+
+static thread_local char g_error_detail[512] = "";
+
+void set_error_detail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error_detail, sizeof(g_error_detail), fmt, ap);
+    va_end(ap);
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace q8k
+
+using namespace q8k;
+
+extern "C" int q8k_version(void) { return 100; }
+
+extern "C" const char* q8k_error_string(int code) {
+    switch (code) {
+        case Q8K_OK: return "ok";
+        case Q8K_ERR_INVALID_ARG: return "invalid argument";
+        case Q8K_ERR_UNSUPPORTED: return "unsupported dtype or shape";
+        case Q8K_ERR_WORKSPACE: return "workspace too small";
+        case Q8K_ERR_CUDA: return "CUDA call failed";
+        case Q8K_ERR_TOO_LARGE: return "problem exceeds a built-in capacity";
+        default: return "unknown error";
+    }
+}
+
+extern "C" const char* q8k_last_error_detail(void) { return g_error_detail; }
+
+extern "C" size_t q8k_linear_workspace_bytes(int M, int K) {
+    if (M <= 0 || K <= 0) return 0;
+    return align_up((size_t)M * (size_t)K, 256) + align_up((size_t)M * sizeof(float), 256);
+}
+
+extern "C" int q8k_linear(const void* x, int x_dtype, const void* w, int w_dtype, const float* w_scales,
+                          const float* bias, void* out, int out_dtype, int M, int N, int K,
+                          int use_hadamard, int fuse_gelu, void* workspace, size_t workspace_bytes,
+                          int* dev_status, void* stream) {
+    Q8K_REQUIRE(M >= 0 && N > 0 && K > 0, Q8K_ERR_INVALID_ARG, "linear: bad shape M=%d N=%d K=%d", M, N, K);
+    if (M == 0) return Q8K_OK;
+    Q8K_REQUIRE(w_dtype == Q8K_DT_I8 || w_dtype == Q8K_DT_E4M3, Q8K_ERR_UNSUPPORTED,
+                "linear: weight dtype %d is not int8 or e4m3", w_dtype);
+    Q8K_REQUIRE(workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0, Q8K_ERR_INVALID_ARG,
+                "linear: workspace must be non-null and 256-byte aligned");
+    Q8K_REQUIRE(workspace_bytes >= q8k_linear_workspace_bytes(M, K), Q8K_ERR_WORKSPACE,
+                "linear: workspace of %zu bytes is smaller than the %zu needed for M=%d K=%d", workspace_bytes,
+                q8k_linear_workspace_bytes(M, K), M, K);
+    void* xq = workspace;
+    float* x_scales = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up((size_t)M * K, 256));
+    int rc;
+    if (use_hadamard) {
+        rc = q8k_hadamard_quant(x, x_dtype, xq, w_dtype, x_scales, M, K, K, (float)(1.0 / sqrt((double)K)), stream);
+    } else {
+        rc = q8k_tokenwise_quant(x, x_dtype, xq, w_dtype, x_scales, M, K, K, stream);
+    }
+    if (rc != Q8K_OK) return rc;
+    if (w_dtype == Q8K_DT_I8)
+        return q8k_q8_mm(xq, w, bias, x_scales, w_scales, out, out_dtype, 1, 1, M, N, K, fuse_gelu, dev_status, stream);
+    return q8k_fp8_mm(xq, w, bias, x_scales, w_scales, out, out_dtype, 1, 1, M, N, K, fuse_gelu, dev_status, stream);
+}

@@ -1,0 +1,167 @@
+// Shared helpers for the sm_100a kernels: error reporting for the C ABI,
+// element-type tags, 8-bit casts with the two rounding flavours the reference
+// uses, and small vector load/store utilities.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/q8_kernels_b200.h"
+
+namespace q8k {
+
+// ---------------------------------------------------------------- host-side errors
+void set_error_detail(const char* fmt, ...);
+
+#define Q8K_REQUIRE(cond, code, ...)                      \
+    do {                                                  \
+        if (!(cond)) {                                    \
+            q8k::set_error_detail(__VA_ARGS__);           \
+            return (code);                                \
+        }                                                 \
+    } while (0)
+
+#define Q8K_CUDA_OK(expr)                                                          \
+    do {                                                                           \
+        cudaError_t _e = (expr);                                                   \
+        if (_e != cudaSuccess) {                                                   \
+            q8k::set_error_detail("%s failed: %s", #expr, cudaGetErrorString(_e)); \
+            return Q8K_ERR_CUDA;                                                   \
+        }                                                                          \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---------------------------------------------------------------- element types
+struct e4m3_t { uint8_t bits; };
+
+template <int DT> struct DType;
+template <> struct DType<Q8K_DT_F32>  { using type = float; };
+template <> struct DType<Q8K_DT_F16>  { using type = __half; };
+template <> struct DType<Q8K_DT_BF16> { using type = __nv_bfloat16; };
+template <> struct DType<Q8K_DT_E4M3> { using type = e4m3_t; };
+template <> struct DType<Q8K_DT_I8>   { using type = int8_t; };
+
+inline int dtype_size(int dt) {
+    switch (dt) {
+        case Q8K_DT_F32: return 4;
+        case Q8K_DT_F16: case Q8K_DT_BF16: return 2;
+        case Q8K_DT_E4M3: case Q8K_DT_I8: return 1;
+        default: return 0;
+    }
+}
+
+// ---------------------------------------------------------------- scalar conversions
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw(v, __NV_E4M3);
+    return __half2float(__half(h));
+}
+
+// fp32 -> e4m3, round to nearest even, saturating to +-448 (cvt.rn.satfinite).
+// Used by the GEMM epilogue and inside attention.
+__device__ __forceinline__ uint8_t float_to_e4m3_sat(float x) {
+    return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ uint16_t float2_to_e4m3x2_sat(float lo, float hi) {
+    return (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+}
+
+// fp32 -> e4m3 the way the c10 software cast does it: round to nearest even,
+// and anything that rounds beyond 448 (|x| > 464, inf, NaN) becomes NaN with
+// the sign kept.  For |x| <= 464 this equals the saturating hardware cast.
+__device__ __forceinline__ uint8_t float_to_e4m3_c10(float x) {
+    uint8_t r = float_to_e4m3_sat(x);
+    const bool overflow = !(fabsf(x) <= 464.0f);          // true for NaN as well
+    if (overflow) r = (uint8_t)(0x7F | ((__float_as_uint(x) >> 24) & 0x80));
+    return r;
+}
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_float<e4m3_t>(e4m3_t v) { return e4m3_to_float(v.bits); }
+template <> __device__ __forceinline__ float to_float<int8_t>(int8_t v) { return (float)v; }
+
+// "plain C++ conversion" of the SIMT ops: bf16/fp16 RNE, e4m3 c10-style.
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ e4m3_t from_float<e4m3_t>(float v) { return e4m3_t{float_to_e4m3_c10(v)}; }
+
+// ---------------------------------------------------------------- vector access
+// N consecutive elements of T <-> fp32 registers.  N * sizeof(T) must be 4, 8,
+// 16 or 32 bytes and the address aligned to min(16, N*sizeof(T)).
+template <int BYTES> struct Vec;
+template <> struct Vec<2>  { using type = uint16_t; };
+template <> struct Vec<4>  { using type = uint32_t; };
+template <> struct Vec<8>  { using type = uint2; };
+template <> struct Vec<16> { using type = uint4; };
+
+template <typename T, int N>
+__device__ __forceinline__ void load_vec(const T* __restrict__ p, float (&out)[N]) {
+    constexpr int BYTES = N * sizeof(T);
+    if constexpr (BYTES <= 16) {
+        using V = typename Vec<BYTES>::type;
+        union { V v; T e[N]; } u;
+        u.v = *reinterpret_cast<const V*>(p);
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[i] = to_float<T>(u.e[i]);
+    } else {
+        static_assert(BYTES % 16 == 0, "vector width");
+        constexpr int PER = 16 / sizeof(T);
+#pragma unroll
+        for (int c = 0; c < BYTES / 16; ++c) {
+            union { uint4 v; T e[PER]; } u;
+            u.v = reinterpret_cast<const uint4*>(p)[c];
+#pragma unroll
+            for (int i = 0; i < PER; ++i) out[c * PER + i] = to_float<T>(u.e[i]);
+        }
+    }
+}
+
+template <typename T, int N>
+__device__ __forceinline__ void store_vec(T* __restrict__ p, const float (&in)[N]) {
+    constexpr int BYTES = N * sizeof(T);
+    if constexpr (BYTES <= 16) {
+        using V = typename Vec<BYTES>::type;
+        union { V v; T e[N]; } u;
+#pragma unroll
+        for (int i = 0; i < N; ++i) u.e[i] = from_float<T>(in[i]);
+        *reinterpret_cast<V*>(p) = u.v;
+    } else {
+        static_assert(BYTES % 16 == 0, "vector width");
+        constexpr int PER = 16 / sizeof(T);
+#pragma unroll
+        for (int c = 0; c < BYTES / 16; ++c) {
+            union { uint4 v; T e[PER]; } u;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) u.e[i] = from_float<T>(in[c * PER + i]);
+            reinterpret_cast<uint4*>(p)[c] = u.v;
+        }
+    }
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// tanh-GELU of the reference (csrc/gemm/q8_matmul_bias.cu:29-33).
+__device__ __forceinline__ float gelu_tanh_precise(float x) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(u));
+}
+
+}  // namespace q8k

@@ -1,0 +1,360 @@
+// HBM-bound row-wise kernels: per-token absmax quantizer, RMS norm, rotary
+// embedding, mixed-precision FMA and tanh-GELU.
+//
+// Layout: every tensor is [rows, dim] with dim contiguous.  One CTA of T
+// threads owns one row; a thread owns ITEMS "items" of 8 consecutive elements
+// (item index t, t+T, ...), so every global access is a 16-byte (bf16), 8-byte
+// (8-bit) or 32-byte (fp32) vector and a warp covers a contiguous segment.
+// The row lives in registers between the reduction and the output pass, so HBM
+// sees each element exactly once in and once out.
+//
+// No fast-math: the quantizer must reproduce IEEE division and C round().
+
+#include "common.cuh"
+
+namespace q8k {
+
+constexpr int kItem = 8;
+
+template <int T>
+__device__ __forceinline__ float block_reduce_max(float v, float* smem) {
+    v = warp_max(v);
+    if constexpr (T > 32) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) smem[warp] = v;
+        __syncthreads();
+        float r = smem[0];
+#pragma unroll
+        for (int w = 1; w < T / 32; ++w) r = fmaxf(r, smem[w]);
+        __syncthreads();
+        v = r;
+    }
+    return v;
+}
+
+template <int T>
+__device__ __forceinline__ float block_reduce_sum(float v, float* smem) {
+    v = warp_sum(v);
+    if constexpr (T > 32) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) smem[warp] = v;
+        __syncthreads();
+        float r = smem[0];
+#pragma unroll
+        for (int w = 1; w < T / 32; ++w) r += smem[w];
+        __syncthreads();
+        v = r;
+    }
+    return v;
+}
+
+// ------------------------------------------------------------------ quantizer
+// Semantics of tokenwise_quantization_kernel
+// (csrc/quantizer/tokenwise_quant_cuda.cu:115-148) with IEEE arithmetic.
+template <typename Tin, typename Tout, int ITEMS, int T>
+__global__ void __launch_bounds__(T)
+tokenwise_quant_kernel(const Tin* __restrict__ x, Tout* __restrict__ q, float* __restrict__ scales,
+                       int dim, int64_t x_row_stride) {
+    __shared__ float red[32];
+    const int64_t row = blockIdx.x;
+    const Tin* xr = x + row * x_row_stride;
+    Tout* qr = q + row * (int64_t)dim;
+
+    float v[ITEMS][kItem];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int e = (threadIdx.x + i * T) * kItem;
+        if (e < dim) {
+            load_vec<Tin, kItem>(xr + e, v[i]);
+#pragma unroll
+            for (int j = 0; j < kItem; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+        }
+    }
+    amax = block_reduce_max<T>(amax, red);
+
+    constexpr bool kInt8 = sizeof(Tout) == 1 && !__is_same(Tout, e4m3_t);
+    const float qmax = kInt8 ? 127.0f : 448.0f;
+    const float scale = __fdiv_rn(qmax, amax);            // +inf for an all-zero row
+    const bool zero_row = amax == 0.f;
+
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int e = (threadIdx.x + i * T) * kItem;
+        if (e < dim) {
+            union { uint2 v2; uint8_t b[kItem]; } o;
+#pragma unroll
+            for (int j = 0; j < kItem; ++j) {
+                const float y = zero_row ? 0.f : __fmul_rn(v[i][j], scale);
+                if constexpr (kInt8) {
+                    o.b[j] = (uint8_t)(int8_t)(int)roundf(y);      // round half away from zero
+                } else {
+                    o.b[j] = float_to_e4m3_c10(y);
+                }
+            }
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(qr) + e) = o.v2;
+        }
+    }
+    if (threadIdx.x == 0) scales[row] = __fdiv_rn(1.0f, scale);
+}
+
+// ------------------------------------------------------------------ RMS norm
+// rms_norm_kernel (csrc/ops/rms_norm_cuda.cu:127-169): no eps, (x*r)*w.
+template <typename Tin, typename Tout, int ITEMS, int T>
+__global__ void __launch_bounds__(T)
+rms_norm_kernel(const Tin* __restrict__ x, const float* __restrict__ w, Tout* __restrict__ out,
+                float* __restrict__ rrms, int dim) {
+    __shared__ float red[32];
+    const int64_t row = blockIdx.x;
+    const Tin* xr = x + row * (int64_t)dim;
+    Tout* outr = out + row * (int64_t)dim;
+
+    float v[ITEMS][kItem];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int e = (threadIdx.x + i * T) * kItem;
+        if (e < dim) {
+            load_vec<Tin, kItem>(xr + e, v[i]);
+#pragma unroll
+            for (int j = 0; j < kItem; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+        }
+    }
+    ss = block_reduce_sum<T>(ss, red);
+    const float r = rsqrtf(ss * (1.0f / (float)dim));
+
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int e = (threadIdx.x + i * T) * kItem;
+        if (e < dim) {
+            float o[kItem];
+            if (w != nullptr) {
+                float wv[kItem];
+                load_vec<float, kItem>(w + e, wv);
+#pragma unroll
+                for (int j = 0; j < kItem; ++j) o[j] = __fmul_rn(__fmul_rn(v[i][j], r), wv[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < kItem; ++j) o[j] = __fmul_rn(v[i][j], r);
+            }
+            store_vec<Tout, kItem>(outr + e, o);
+        }
+    }
+    if (rrms != nullptr && threadIdx.x == 0) rrms[row] = r;
+}
+
+// ------------------------------------------------------------------ element-wise rows
+// These keep nothing between passes, so a CTA strides over a row in items and
+// the grid is rows x ceil(items / T).
+
+// rope_kernel (csrc/ops/rope_cuda.cu:99-103), products rounded before the add.
+template <typename Tin, typename Tout, int T>
+__global__ void __launch_bounds__(T)
+rope_kernel(const Tin* __restrict__ x, const float* __restrict__ cosf_, const float* __restrict__ sinf_,
+            Tout* __restrict__ out, int dim, int64_t freq_rows) {
+    const int64_t row = blockIdx.x;
+    const int e = (blockIdx.y * T + threadIdx.x) * kItem;
+    if (e >= dim) return;
+    const int64_t frow = freq_rows > 0 ? row % freq_rows : row;
+    float xv[kItem], c[kItem], s[kItem], o[kItem];
+    load_vec<Tin, kItem>(x + row * (int64_t)dim + e, xv);
+    load_vec<float, kItem>(cosf_ + frow * (int64_t)dim + e, c);
+    load_vec<float, kItem>(sinf_ + frow * (int64_t)dim + e, s);
+#pragma unroll
+    for (int j = 0; j < kItem; j += 2) {
+        o[j]     = __fadd_rn(__fmul_rn(-xv[j + 1], s[j]), __fmul_rn(xv[j], c[j]));
+        o[j + 1] = __fadd_rn(__fmul_rn(xv[j], s[j + 1]), __fmul_rn(xv[j + 1], c[j + 1]));
+    }
+    store_vec<Tout, kItem>(out + row * (int64_t)dim + e, o);
+}
+
+// fma_kernel (csrc/ops/fma_cuda.cu:92-95).
+template <typename Ty, typename Tz, int T>
+__global__ void __launch_bounds__(T)
+fma_kernel(const e4m3_t* __restrict__ x, const Ty* __restrict__ y, const Tz* __restrict__ z,
+           e4m3_t* __restrict__ out, int dim, int64_t y_every, int64_t z_every, float scale_add) {
+    const int64_t row = blockIdx.x;
+    const int e = (blockIdx.y * T + threadIdx.x) * kItem;
+    if (e >= dim) return;
+    float xv[kItem], yv[kItem], zv[kItem], o[kItem];
+    load_vec<e4m3_t, kItem>(x + row * (int64_t)dim + e, xv);
+    load_vec<Ty, kItem>(y + (row / y_every) * (int64_t)dim + e, yv);
+    load_vec<Tz, kItem>(z + (row / z_every) * (int64_t)dim + e, zv);
+#pragma unroll
+    for (int j = 0; j < kItem; ++j)
+        o[j] = __fadd_rn(__fmul_rn(xv[j], __fadd_rn(yv[j], scale_add)), zv[j]);
+    store_vec<e4m3_t, kItem>(out + row * (int64_t)dim + e, o);
+}
+
+// gelu_forward_kernel (csrc/ops/gelu_forward_cuda.cu:12-16).
+template <typename Tin, typename Tout, int T>
+__global__ void __launch_bounds__(T)
+gelu_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, int dim) {
+    const int64_t row = blockIdx.x;
+    const int e = (blockIdx.y * T + threadIdx.x) * kItem;
+    if (e >= dim) return;
+    float xv[kItem], o[kItem];
+    load_vec<Tin, kItem>(x + row * (int64_t)dim + e, xv);
+#pragma unroll
+    for (int j = 0; j < kItem; ++j) o[j] = gelu_tanh_precise(xv[j]);
+    store_vec<Tout, kItem>(out + row * (int64_t)dim + e, o);
+}
+
+// ------------------------------------------------------------------ launch helpers
+template <typename Tin, typename Tout>
+static int launch_quant(const void* x, void* q, float* scales, int64_t rows, int dim,
+                        int64_t stride, cudaStream_t st) {
+    const int items = dim / kItem;
+#define Q8K_Q_LAUNCH(ITEMS, T)                                                                  \
+    tokenwise_quant_kernel<Tin, Tout, ITEMS, T><<<(unsigned)rows, T, 0, st>>>(                   \
+        (const Tin*)x, (Tout*)q, scales, dim, stride)
+    if (items <= 32)        Q8K_Q_LAUNCH(1, 32);
+    else if (items <= 128)  Q8K_Q_LAUNCH(1, 128);
+    else if (items <= 256)  Q8K_Q_LAUNCH(2, 128);
+    else if (items <= 512)  Q8K_Q_LAUNCH(4, 128);
+    else if (items <= 1024) Q8K_Q_LAUNCH(4, 256);
+    else if (items <= 2048) Q8K_Q_LAUNCH(8, 256);
+    else if (items <= 4096) Q8K_Q_LAUNCH(8, 512);
+    else { set_error_detail("tokenwise_quant: dim %d exceeds 32768", dim); return Q8K_ERR_UNSUPPORTED; }
+#undef Q8K_Q_LAUNCH
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+template <typename Tin, typename Tout>
+static int launch_rms(const void* x, const float* w, void* out, float* rrms, int64_t rows, int dim,
+                      cudaStream_t st) {
+    const int items = dim / kItem;
+#define Q8K_R_LAUNCH(ITEMS, T)                                                                  \
+    rms_norm_kernel<Tin, Tout, ITEMS, T><<<(unsigned)rows, T, 0, st>>>(                          \
+        (const Tin*)x, w, (Tout*)out, rrms, dim)
+    if (items <= 32)        Q8K_R_LAUNCH(1, 32);
+    else if (items <= 128)  Q8K_R_LAUNCH(1, 128);
+    else if (items <= 256)  Q8K_R_LAUNCH(2, 128);
+    else if (items <= 512)  Q8K_R_LAUNCH(4, 128);
+    else if (items <= 1024) Q8K_R_LAUNCH(4, 256);
+    else if (items <= 2048) Q8K_R_LAUNCH(8, 256);
+    else if (items <= 4096) Q8K_R_LAUNCH(8, 512);
+    else { set_error_detail("rms_norm: dim %d exceeds 32768", dim); return Q8K_ERR_UNSUPPORTED; }
+#undef Q8K_R_LAUNCH
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+static int check_rows_dim(const char* op, int64_t rows, int dim, int multiple) {
+    Q8K_REQUIRE(rows >= 0 && rows <= 0x7fffffffLL, Q8K_ERR_INVALID_ARG, "%s: rows %lld out of range", op, (long long)rows);
+    Q8K_REQUIRE(dim > 0 && dim % multiple == 0, Q8K_ERR_INVALID_ARG,
+                "%s: dim %d must be a positive multiple of %d", op, dim, multiple);
+    return Q8K_OK;
+}
+
+}  // namespace q8k
+
+using namespace q8k;
+
+extern "C" int q8k_tokenwise_quant(const void* x, int x_dtype, void* q, int q_dtype, float* scales,
+                                   int64_t rows, int dim, int64_t x_row_stride, void* stream) {
+    if (int rc = check_rows_dim("tokenwise_quant", rows, dim, 16)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(x && q && scales, Q8K_ERR_INVALID_ARG, "tokenwise_quant: null pointer");
+    Q8K_REQUIRE(aligned16(x) && aligned16(q), Q8K_ERR_INVALID_ARG, "tokenwise_quant: x and q must be 16-byte aligned");
+    Q8K_REQUIRE(x_row_stride >= dim && (x_row_stride * dtype_size(x_dtype)) % 16 == 0, Q8K_ERR_INVALID_ARG,
+                "tokenwise_quant: row stride %lld must be >= dim and a multiple of 16 bytes", (long long)x_row_stride);
+    Q8K_REQUIRE(q_dtype == Q8K_DT_I8 || q_dtype == Q8K_DT_E4M3, Q8K_ERR_UNSUPPORTED,
+                "tokenwise_quant: output dtype %d is not int8 or e4m3", q_dtype);
+    cudaStream_t st = (cudaStream_t)stream;
+#define Q8K_QD(TIN)                                                                              \
+    return q_dtype == Q8K_DT_I8 ? launch_quant<TIN, int8_t>(x, q, scales, rows, dim, x_row_stride, st) \
+                                : launch_quant<TIN, e4m3_t>(x, q, scales, rows, dim, x_row_stride, st)
+    switch (x_dtype) {
+        case Q8K_DT_F32:  Q8K_QD(float);
+        case Q8K_DT_F16:  Q8K_QD(__half);
+        case Q8K_DT_BF16: Q8K_QD(__nv_bfloat16);
+        case Q8K_DT_E4M3: Q8K_QD(e4m3_t);
+        default: break;
+    }
+#undef Q8K_QD
+    set_error_detail("tokenwise_quant: input dtype %d not supported", x_dtype);
+    return Q8K_ERR_UNSUPPORTED;
+}
+
+extern "C" int q8k_rms_norm(const void* x, int x_dtype, const float* weights, void* out, int out_dtype,
+                            float* rrms, int64_t rows, int dim, void* stream) {
+    if (int rc = check_rows_dim("rms_norm", rows, dim, 16)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(x && out, Q8K_ERR_INVALID_ARG, "rms_norm: null pointer");
+    Q8K_REQUIRE(aligned16(x) && aligned16(out) && aligned16(weights), Q8K_ERR_INVALID_ARG,
+                "rms_norm: pointers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dtype == Q8K_DT_BF16 && out_dtype == Q8K_DT_BF16) return launch_rms<__nv_bfloat16, __nv_bfloat16>(x, weights, out, rrms, rows, dim, st);
+    if (x_dtype == Q8K_DT_BF16 && out_dtype == Q8K_DT_E4M3) return launch_rms<__nv_bfloat16, e4m3_t>(x, weights, out, rrms, rows, dim, st);
+    if (x_dtype == Q8K_DT_E4M3 && out_dtype == Q8K_DT_BF16) return launch_rms<e4m3_t, __nv_bfloat16>(x, weights, out, rrms, rows, dim, st);
+    if (x_dtype == Q8K_DT_E4M3 && out_dtype == Q8K_DT_E4M3) return launch_rms<e4m3_t, e4m3_t>(x, weights, out, rrms, rows, dim, st);
+    set_error_detail("rms_norm: dtype pair (%d -> %d) not supported", x_dtype, out_dtype);
+    return Q8K_ERR_UNSUPPORTED;
+}
+
+extern "C" int q8k_rope(const void* x, int x_dtype, const float* cos_freqs, const float* sin_freqs,
+                        void* out, int out_dtype, int64_t rows, int dim, int64_t freq_rows, void* stream) {
+    if (int rc = check_rows_dim("rope", rows, dim, 16)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(x && out && cos_freqs && sin_freqs, Q8K_ERR_INVALID_ARG, "rope: null pointer");
+    Q8K_REQUIRE(aligned16(x) && aligned16(out) && aligned16(cos_freqs) && aligned16(sin_freqs),
+                Q8K_ERR_INVALID_ARG, "rope: pointers must be 16-byte aligned");
+    Q8K_REQUIRE(freq_rows >= 0, Q8K_ERR_INVALID_ARG, "rope: freq_rows must be >= 0");
+    cudaStream_t st = (cudaStream_t)stream;
+    constexpr int T = 128;
+    dim3 grid((unsigned)rows, (unsigned)((dim / kItem + T - 1) / T));
+#define Q8K_ROPE(TIN, TOUT) rope_kernel<TIN, TOUT, T><<<grid, T, 0, st>>>((const TIN*)x, cos_freqs, sin_freqs, (TOUT*)out, dim, freq_rows)
+    if (x_dtype == Q8K_DT_BF16 && out_dtype == Q8K_DT_BF16) Q8K_ROPE(__nv_bfloat16, __nv_bfloat16);
+    else if (x_dtype == Q8K_DT_BF16 && out_dtype == Q8K_DT_E4M3) Q8K_ROPE(__nv_bfloat16, e4m3_t);
+    else if (x_dtype == Q8K_DT_BF16 && out_dtype == Q8K_DT_F32) Q8K_ROPE(__nv_bfloat16, float);
+    else if (x_dtype == Q8K_DT_E4M3 && out_dtype == Q8K_DT_BF16) Q8K_ROPE(e4m3_t, __nv_bfloat16);
+    else if (x_dtype == Q8K_DT_E4M3 && out_dtype == Q8K_DT_E4M3) Q8K_ROPE(e4m3_t, e4m3_t);
+    else { set_error_detail("rope: dtype pair (%d -> %d) not supported", x_dtype, out_dtype); return Q8K_ERR_UNSUPPORTED; }
+#undef Q8K_ROPE
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_fma_8bit(const void* x, const void* y, int y_dtype, const void* z, int z_dtype, void* out,
+                            int64_t rows, int dim, int64_t y_every, int64_t z_every, float scale_add,
+                            void* stream) {
+    if (int rc = check_rows_dim("fma_8bit", rows, dim, 16)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(x && y && z && out, Q8K_ERR_INVALID_ARG, "fma_8bit: null pointer");
+    Q8K_REQUIRE(aligned16(x) && aligned16(y) && aligned16(z) && aligned16(out), Q8K_ERR_INVALID_ARG,
+                "fma_8bit: pointers must be 16-byte aligned");
+    Q8K_REQUIRE(y_every >= 1 && z_every >= 1, Q8K_ERR_INVALID_ARG, "fma_8bit: broadcast periods must be >= 1");
+    cudaStream_t st = (cudaStream_t)stream;
+    constexpr int T = 128;
+    dim3 grid((unsigned)rows, (unsigned)((dim / kItem + T - 1) / T));
+#define Q8K_FMA(TY, TZ) fma_kernel<TY, TZ, T><<<grid, T, 0, st>>>((const e4m3_t*)x, (const TY*)y, (const TZ*)z, (e4m3_t*)out, dim, y_every, z_every, scale_add)
+    if (y_dtype == Q8K_DT_F32 && z_dtype == Q8K_DT_F32) Q8K_FMA(float, float);
+    else if (y_dtype == Q8K_DT_F32 && z_dtype == Q8K_DT_E4M3) Q8K_FMA(float, e4m3_t);
+    else if (y_dtype == Q8K_DT_BF16 && z_dtype == Q8K_DT_BF16) Q8K_FMA(__nv_bfloat16, __nv_bfloat16);
+    else { set_error_detail("fma_8bit: (y,z) dtypes (%d,%d) not supported", y_dtype, z_dtype); return Q8K_ERR_UNSUPPORTED; }
+#undef Q8K_FMA
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_gelu_forward(const void* x, int x_dtype, void* out, int out_dtype, int64_t rows, int dim,
+                                void* stream) {
+    if (int rc = check_rows_dim("gelu_forward", rows, dim, 16)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(x && out, Q8K_ERR_INVALID_ARG, "gelu_forward: null pointer");
+    Q8K_REQUIRE(aligned16(x) && aligned16(out), Q8K_ERR_INVALID_ARG, "gelu_forward: pointers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    constexpr int T = 128;
+    dim3 grid((unsigned)rows, (unsigned)((dim / kItem + T - 1) / T));
+#define Q8K_GELU(TIN, TOUT) gelu_kernel<TIN, TOUT, T><<<grid, T, 0, st>>>((const TIN*)x, (TOUT*)out, dim)
+    if (x_dtype == Q8K_DT_BF16 && out_dtype == Q8K_DT_BF16) Q8K_GELU(__nv_bfloat16, __nv_bfloat16);
+    else if (x_dtype == Q8K_DT_BF16 && out_dtype == Q8K_DT_E4M3) Q8K_GELU(__nv_bfloat16, e4m3_t);
+    else if (x_dtype == Q8K_DT_E4M3 && out_dtype == Q8K_DT_BF16) Q8K_GELU(e4m3_t, __nv_bfloat16);
+    else if (x_dtype == Q8K_DT_E4M3 && out_dtype == Q8K_DT_E4M3) Q8K_GELU(e4m3_t, e4m3_t);
+    else { set_error_detail("gelu_forward: dtype pair (%d -> %d) not supported", x_dtype, out_dtype); return Q8K_ERR_UNSUPPORTED; }
+#undef Q8K_GELU
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}

@@ -1,0 +1,145 @@
+"""Generate the committed fixtures under tests/golden/.
+
+Two kinds of file:
+
+* ``ref_*.npz`` -- produced by importing the reference's own pure-torch code
+  from a checkout of KONAKONA666/q8_kernels (path in $Q8_REFERENCE, default
+  /root/reference): ``apply_rope`` (q8_kernels/functional/rope.py:25-43, the
+  path the reference really runs) and ``precompute_freqs_cis``
+  (q8_kernels/models/LTXVideo.py:86-148).  Their native and diffusers imports
+  are replaced by inert stubs; only torch arithmetic of the reference executes.
+  These pin the oracle's RoPE and RoPE-table restatements.
+* ``oracle_*.npz`` -- small seeded cases run through oracle/q8_oracle.py, kept
+  so that the GPU kernels are also checked against frozen vectors and a change
+  of the oracle shows up as a diff.  The reference has no tests or vectors for
+  these ops, so they are NOT pinned by the reference.
+
+Usage:  python tests/golden/make_golden.py
+"""
+import importlib.util
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from oracle import q8_oracle as O  # noqa: E402
+import helpers as Hp  # noqa: E402
+
+REF = os.environ.get("Q8_REFERENCE", "/root/reference")
+
+
+def _np(t: torch.Tensor) -> np.ndarray:
+    """Store tensors losslessly: bf16 as int16 bits, e4m3/int8 as uint8/int8."""
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy()
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8).numpy()
+    return t.numpy()
+
+
+def _stub(name: str, **attrs) -> types.ModuleType:
+    m = types.ModuleType(name)
+    for k, v in attrs.items():
+        setattr(m, k, v)
+    sys.modules[name] = m
+    return m
+
+
+def _load(path: str, name: str):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def reference_fixtures() -> None:
+    unavailable = lambda *a, **k: (_ for _ in ()).throw(RuntimeError("native stub"))  # noqa: E731
+    _stub("q8_kernels_cuda")
+    _stub("q8_kernels_cuda.ops")
+    _stub("q8_kernels_cuda.ops._C", rope=unavailable, rope_backward=unavailable)
+    ref_rope = _load(os.path.join(REF, "q8_kernels/functional/rope.py"), "ref_rope")
+
+    ident = lambda f: f  # noqa: E731
+    _stub("diffusers")
+    _stub("diffusers.configuration_utils", ConfigMixin=object, register_to_config=ident)
+    _stub("diffusers.models")
+    _stub("diffusers.models.embeddings", PixArtAlphaTextProjection=object)
+    _stub("diffusers.models.modeling_utils", ModelMixin=torch.nn.Module)
+    _stub("diffusers.models.normalization", AdaLayerNormSingle=object)
+    _stub("diffusers.utils", BaseOutput=object, is_torch_version=lambda *a: True,
+          logging=types.SimpleNamespace(get_logger=lambda n: None))
+    _stub("q8_kernels")
+    _stub("q8_kernels.blocks")
+    _stub("q8_kernels.blocks.ltx_transformer_block", LTXTransformerBlock=object)
+    ref_ltx = _load(os.path.join(REF, "q8_kernels/models/LTXVideo.py"), "ref_ltx")
+
+    # RoPE table for a 2 x 3 x 4 latent grid at the model's hyper-parameters
+    cls = ref_ltx.LTXTransformer3DModel
+    fake = types.SimpleNamespace(inner_dim=2048, positional_embedding_theta=10000.0,
+                                 positional_embedding_max_pos=[20, 2048, 2048])
+    fake.get_fractional_positions = lambda g: cls.get_fractional_positions(fake, g)
+    t, h, w = torch.meshgrid(torch.arange(2), torch.arange(3), torch.arange(4), indexing="ij")
+    grid = torch.stack([t.flatten(), h.flatten(), w.flatten()], dim=0).unsqueeze(0).float()     # [1,3,24]
+    cos, sin = cls.precompute_freqs_cis(fake, grid)
+    np.savez_compressed(os.path.join(HERE, "ref_freqs_cis.npz"), grid=grid.numpy(), cos=cos.numpy(), sin=sin.numpy())
+
+    x = Hp.activations(24, 2048, seed=901).reshape(1, 24, 2048)
+    out = ref_rope.apply_rope(x, cos, sin)
+    np.savez_compressed(os.path.join(HERE, "ref_rope.npz"), x=_np(x), cos=cos.numpy(), sin=sin.numpy(),
+                        out=out.numpy())
+    print("reference fixtures:", tuple(cos.shape), out.dtype)
+
+
+def oracle_fixtures() -> None:
+    E4M3 = torch.float8_e4m3fn
+    # quantizer
+    x = Hp.activations(16, 256, seed=11)
+    x[3] = 0                                               # all-zero row: defined edge case
+    q8, s8 = O.tokenwise_quant(x)
+    qf, sf = O.tokenwise_quant(x, E4M3)
+    np.savez_compressed(os.path.join(HERE, "oracle_quant.npz"), x=_np(x), q_i8=_np(q8), s_i8=s8.numpy(),
+                        q_fp8=_np(qf), s_fp8=sf.numpy())
+    # Hadamard (power-of-two and padded dims)
+    cases = {}
+    for dim in (64, 2048, 40):
+        xh = Hp.activations(8, dim, seed=20 + dim)
+        cases[f"x_{dim}"] = _np(xh)
+        cases[f"bf16_{dim}"] = _np(O.hadamard_transform(xh))
+        cases[f"fp8_{dim}"] = _np(O.hadamard_transform(xh, scale=0.0442, out_dtype=E4M3))
+    np.savez_compressed(os.path.join(HERE, "oracle_hadamard.npz"), **cases)
+    # GEMM (int8 and fp8, bias + GELU, bf16 out)
+    a = Hp.activations(96, 256, seed=31)
+    w = Hp.weights(128, 256, seed=32)
+    b = Hp.bias_vec(128, seed=33)
+    aq, sa = O.tokenwise_quant(O.hadamard_transform(a))
+    wq, sw = O.tokenwise_quant(O.hadamard_transform(w))
+    y_i8 = O.q8_mm(aq, wq, sa, sw, True, torch.bfloat16, bias=b)
+    af, saf = O.tokenwise_quant(a, E4M3)
+    wf, swf = O.tokenwise_quant(w, E4M3)
+    y_f8 = O.fp8_mm(af, wf, saf, swf, True, torch.bfloat16, bias=b)
+    np.savez_compressed(os.path.join(HERE, "oracle_gemm.npz"), a=_np(a), w=_np(w), bias=b.numpy(),
+                        aq=_np(aq), sa=sa.numpy(), wq=_np(wq), sw=sw.numpy(), y_i8=_np(y_i8),
+                        af=_np(af), saf=saf.numpy(), wf=_np(wf), swf=swf.numpy(), y_f8=_np(y_f8))
+    # attention (self, ragged length, masked)
+    q, k, v = Hp.qkv(1, 2, 200, 64, seed=41)
+    o_self = O.flash_attn_func(q, k, v, apply_qk_hadamard=True, out_dtype=torch.bfloat16)
+    mask = torch.tensor([77], dtype=torch.int32)
+    o_mask = O.flash_attn_func(q, k, v, batch_mask=mask, apply_qk_hadamard=True, out_dtype=torch.bfloat16)
+    np.savez_compressed(os.path.join(HERE, "oracle_attention.npz"), q=_np(q.contiguous()), k=_np(k.contiguous()),
+                        v=_np(v.contiguous()), o_self=_np(o_self), mask=mask.numpy(), o_mask=_np(o_mask))
+    print("oracle fixtures written")
+
+
+if __name__ == "__main__":
+    if os.path.isdir(REF):
+        reference_fixtures()
+    else:
+        print(f"{REF} not present: reference fixtures left untouched")
+    oracle_fixtures()

@@ -1,0 +1,223 @@
+"""CPU tests of the oracle: against vectors produced by the reference's own
+pure-torch code (RoPE, RoPE table), against mathematical identities, and
+against the frozen oracle fixtures."""
+import math
+
+import numpy as np
+import pytest
+import scipy.linalg
+import torch
+
+import golden_io as G
+import helpers as Hp
+from oracle import q8_oracle as O
+
+E4M3 = torch.float8_e4m3fn
+
+
+# ------------------------------------------------------------------ pinned by the reference
+def test_rope_matches_reference_vectors():
+    d = G.load("ref_rope.npz")
+    x, cos, sin, ref = G.bf16(d["x"]), G.t(d["cos"]), G.t(d["sin"]), G.t(d["out"])
+    # the torch path the reference runs returns fp32 (torch promotion)
+    out = O.rope(x, cos, sin, out_dtype=torch.float32)
+    Hp.assert_bit_equal(out, ref, "oracle rope vs reference apply_rope")
+    Hp.assert_bit_equal(O.apply_rotary_emb_torch(x, cos, sin), ref, "torch restatement vs reference")
+
+
+def test_freqs_cis_matches_reference_vectors():
+    d = G.load("ref_freqs_cis.npz")
+    cos, sin = O.precompute_freqs_cis(G.t(d["grid"]), dim=2048)
+    Hp.assert_bit_equal(cos, G.t(d["cos"]), "cos table")
+    Hp.assert_bit_equal(sin, G.t(d["sin"]), "sin table")
+    # left padding with cos = 1, sin = 0 for dim % 6 channels
+    assert torch.all(cos[..., :2] == 1) and torch.all(sin[..., :2] == 0)
+
+
+# ------------------------------------------------------------------ casts
+def test_c10_e4m3_cast_known_answers():
+    x = torch.tensor([0.0, 448.0, 464.0, 465.0, -500.0, 2.0 ** -9, 2.0 ** -10, 1.0625, 1.1875, float("inf")])
+    y = O.c10_e4m3(x).float()
+    assert y[0] == 0 and y[1] == 448 and y[2] == 448
+    assert torch.isnan(y[3]) and torch.isnan(y[4]) and torch.isnan(y[9])
+    assert y[5] == 2.0 ** -9 and y[6] == 0.0          # smallest subnormal, then round-to-even down to 0
+    assert y[7] == 1.0 and y[8] == 1.25               # ties to even mantissa
+    s = O.sat_e4m3(torch.tensor([465.0, -1e9, 3.0])).float()
+    assert s.tolist() == [448.0, -448.0, 3.0]
+
+
+def test_round_half_away():
+    x = torch.tensor([0.5, 1.5, 2.5, -0.5, -2.5, 0.49999997, 126.5, -126.5])
+    assert O.round_half_away(x).tolist() == [1.0, 2.0, 3.0, -1.0, -3.0, 0.0, 127.0, -127.0]
+
+
+# ------------------------------------------------------------------ quantizer
+@pytest.mark.parametrize("out_dtype", [torch.int8, E4M3])
+def test_quantizer_properties(out_dtype):
+    x = Hp.activations(32, 2048, seed=1)
+    q, s = O.tokenwise_quant(x, out_dtype)
+    qmax = 127.0 if out_dtype == torch.int8 else 448.0
+    assert q.dtype == out_dtype and s.dtype == torch.float32 and s.shape == (32,)
+    qf = q.float()
+    assert not torch.isnan(qf).any()
+    assert torch.all(qf.abs().amax(dim=1) == qmax)                       # the absmax element maps to QMAX
+    amax = x.float().abs().amax(dim=1)
+    assert torch.allclose(s, amax / qmax, rtol=2e-7, atol=0)
+    err = (qf * s[:, None] - x.float()).abs()
+    step = s[:, None] * (0.5 if out_dtype == torch.int8 else 16.0)        # half an int step / half the top e4m3 ulp
+    assert torch.all(err <= step * 1.0001)
+
+
+def test_quantizer_zero_row_and_default_dtype():
+    x = torch.zeros(2, 64, dtype=torch.bfloat16)
+    x[1, 5] = 3.0
+    q, s = O.tokenwise_quant(x)
+    assert q.dtype == torch.int8
+    assert torch.all(q[0] == 0) and s[0] == 0
+    assert q[1, 5] == 127
+
+
+def test_quantizer_fixture():
+    d = G.load("oracle_quant.npz")
+    x = G.bf16(d["x"])
+    q, s = O.tokenwise_quant(x)
+    Hp.assert_bit_equal(q, G.t(d["q_i8"]), "int8 q")
+    Hp.assert_bit_equal(s, G.t(d["s_i8"]), "int8 scales")
+    q, s = O.tokenwise_quant(x, E4M3)
+    Hp.assert_bit_equal(q, G.e4m3(d["q_fp8"]), "fp8 q")
+    Hp.assert_bit_equal(s, G.t(d["s_fp8"]), "fp8 scales")
+
+
+# ------------------------------------------------------------------ Hadamard
+@pytest.mark.parametrize("dim", [8, 64, 512, 2048])
+def test_hadamard_matches_dense_matrix(dim):
+    # small integers keep every partial sum exact in fp32, so the butterfly
+    # network must equal the dense Sylvester matrix product bit for bit
+    x = torch.randint(-8, 9, (5, dim), generator=Hp.gen(dim)).to(torch.bfloat16)
+    h = torch.tensor(scipy.linalg.hadamard(dim), dtype=torch.float64)
+    want = (x.double() @ h).float()
+    got = O.hadamard_transform(x, scale=1.0, out_dtype=torch.float32)
+    assert torch.equal(got, want)
+
+
+def test_hadamard_involution_and_padding():
+    x = Hp.activations(4, 256, seed=3, outliers=False)
+    y = O.hadamard_transform(x, out_dtype=torch.float32)                  # scale 1/sqrt(n): orthonormal
+    z = O.fwht_fp32(y) / math.sqrt(256)
+    assert O.rel_fro(z, x.float()) < 1e-6
+    xp = Hp.activations(4, 40, seed=4, outliers=False)
+    yp = O.hadamard_transform(xp, scale=1.0, out_dtype=torch.float32)
+    full = O.hadamard_transform(torch.nn.functional.pad(xp, (0, 24)), scale=1.0, out_dtype=torch.float32)
+    assert torch.equal(yp, full[:, :40])
+
+
+def test_hadamard_fixture():
+    d = G.load("oracle_hadamard.npz")
+    for dim in (64, 2048, 40):
+        x = G.bf16(d[f"x_{dim}"])
+        Hp.assert_bit_equal(O.hadamard_transform(x), G.bf16(d[f"bf16_{dim}"]), f"bf16 {dim}")
+        Hp.assert_bit_equal(O.hadamard_transform(x, scale=0.0442, out_dtype=E4M3), G.e4m3(d[f"fp8_{dim}"]),
+                            f"fp8 {dim}")
+
+
+# ------------------------------------------------------------------ GEMM
+def test_gemm_against_float64_dequantised_product():
+    a = Hp.activations(64, 512, seed=5)
+    w = Hp.weights(128, 512, seed=6)
+    b = Hp.bias_vec(128, seed=7)
+    want = a.double() @ w.double().T + b.double()
+    aq, sa = O.tokenwise_quant(a)
+    wq, sw = O.tokenwise_quant(w)
+    y = O.q8_mm(aq, wq, sa, sw, False, torch.bfloat16, bias=b)
+    assert y.shape == (1, 64, 128)
+    assert O.rel_fro(y[0], want) < 0.08                                   # int8 quantisation noise (outlier channels)
+    af, saf = O.tokenwise_quant(a, E4M3)
+    wf, swf = O.tokenwise_quant(w, E4M3)
+    y8 = O.fp8_mm(af, wf, saf, swf, False, torch.bfloat16, bias=b)
+    assert O.rel_fro(y8[0], want) < 0.08
+    # fp32 accumulation vs exact accumulation of the same e4m3 operands
+    assert O.rel_fro(y8, O.fp8_mm(af, wf, saf, swf, False, torch.bfloat16, bias=b, exact=True)) < 2e-3
+
+
+def test_gemm_batch_broadcast_and_default_dtype():
+    aq = torch.randint(-127, 128, (3, 8, 64), generator=Hp.gen(8), dtype=torch.int8)
+    wq = torch.randint(-127, 128, (16, 64), generator=Hp.gen(9), dtype=torch.int8)
+    sa = torch.rand(3, 8, generator=Hp.gen(10)) * 0.01
+    sw = torch.rand(16, generator=Hp.gen(11)) * 0.01
+    y = O.q8_mm(aq, wq, sa, sw)
+    assert y.shape == (3, 8, 16) and y.dtype == E4M3
+    y1 = O.q8_mm(aq[1], wq, sa[1], sw)
+    Hp.assert_bit_equal(y[1], y1[0])
+
+
+def test_gemm_fixture():
+    d = G.load("oracle_gemm.npz")
+    y = O.q8_mm(G.t(d["aq"]), G.t(d["wq"]), G.t(d["sa"]), G.t(d["sw"]), True, torch.bfloat16, bias=G.t(d["bias"]))
+    Hp.assert_bit_equal(y, G.bf16(d["y_i8"]), "int8 gemm")
+    y = O.fp8_mm(G.e4m3(d["af"]), G.e4m3(d["wf"]), G.t(d["saf"]), G.t(d["swf"]), True, torch.bfloat16,
+                 bias=G.t(d["bias"]))
+    assert O.rel_fro(y, G.bf16(d["y_f8"])) < 1e-3       # fp32 BLAS summation order may differ between hosts
+
+
+def test_linear_chain_equals_steps():
+    a = Hp.activations(16, 256, seed=12)
+    w = Hp.weights(32, 256, seed=13)
+    y = O.q8_linear(a, w, None, None, None, False, torch.bfloat16)
+    aq, sa = O.tokenwise_quant(O.hadamard_transform(a))
+    wq, sw = O.tokenwise_quant(O.hadamard_transform(w))
+    Hp.assert_bit_equal(y, O.q8_mm(aq, wq, sa, sw, False, torch.bfloat16))
+    # the Hadamard rotation cancels: result approximates the plain product
+    assert O.rel_fro(y[0], a.double() @ w.double().T) < 0.03
+
+
+# ------------------------------------------------------------------ row-wise ops
+def test_rms_norm_rope_fma_gelu():
+    x = Hp.activations(8, 2048, seed=14)
+    w = torch.rand(2048, generator=Hp.gen(15)) + 0.5
+    y, r = O.rms_norm(x, w, torch.float32)
+    want = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True)) * w.double()
+    assert O.rel_fro(y, want) < 1e-6 and r.shape == (8,)
+    x8 = O.c10_e4m3(torch.randn(2, 4, 64, generator=Hp.gen(16)))
+    yb = torch.randn(2, 1, 64, generator=Hp.gen(17))
+    zb = torch.randn(2, 4, 64, generator=Hp.gen(18))
+    out = O.fma_8bit(x8, yb, zb, 1.0)
+    assert out.dtype == E4M3 and out.shape == (2, 4, 64)
+    assert O.rel_fro(out.float(), x8.float() * (yb + 1) + zb) < 0.05
+    g = O.gelu_forward(torch.tensor([-3.0, 0.0, 1.0, 4.0]).bfloat16(), torch.float32)
+    assert torch.allclose(g, torch.nn.functional.gelu(torch.tensor([-3.0, 0.0, 1.0, 4.0]), approximate="tanh"),
+                          atol=1e-6)
+
+
+# ------------------------------------------------------------------ attention
+def test_attention_oracle_close_to_exact_softmax():
+    q, k, v = Hp.qkv(1, 2, 300, 64, seed=19)
+    o = O.flash_attn_func(q, k, v, apply_qk_hadamard=True, out_dtype=torch.float32)
+    hd = math.sqrt(1 / 64) * math.sqrt(64 ** -0.5)
+    q8 = O.hadamard_transform(q, scale=hd, out_dtype=E4M3)
+    k8 = O.hadamard_transform(k, scale=hd, out_dtype=E4M3)
+    vt = O.c10_e4m3(torch.nn.functional.pad(v.transpose(2, 3), (0, 4)))
+    exact = O.attention_exact(q8, k8, vt, 1.0)
+    assert O.rel_fro(o, exact) < 0.02                                     # e4m3 P noise only
+    # block size moves the result far less than the 2e-3 parity tolerance
+    o128 = O.flash_attention(q8, k8, vt, 1.0, None, torch.float32, block_n=128)
+    assert O.rel_fro(o128, o) < 1e-3
+
+
+def test_attention_mask_semantics():
+    q, k, v = Hp.qkv(2, 2, 96, 64, seed=20)
+    mask = torch.tensor([40, 0], dtype=torch.int32)
+    o = O.flash_attn_func(q, k, v, batch_mask=mask, out_dtype=torch.float32)
+    o40 = O.flash_attn_func(q[:1, :, :, :], k[:1, :, :40], v[:1, :, :40], out_dtype=torch.float32)
+    assert O.rel_fro(o[0], o40[0]) < 5e-3                                 # masked == truncated (up to P rounding)
+    vmean = O.c10_e4m3(v[1]).float().mean(dim=1, keepdim=True)            # valid length 0: plain mean of V rows
+    assert O.rel_fro(o[1], vmean.expand_as(o[1])) < 1e-5
+    assert O.flash_attn_func(q, k, v).dtype == E4M3                       # reference default output dtype
+
+
+def test_attention_fixture():
+    d = G.load("oracle_attention.npz")
+    q, k, v = (G.bf16(d[n]) for n in ("q", "k", "v"))
+    o = O.flash_attn_func(q, k, v, apply_qk_hadamard=True, out_dtype=torch.bfloat16)
+    assert O.rel_fro(o, G.bf16(d["o_self"])) < 1e-3
+    o = O.flash_attn_func(q, k, v, batch_mask=G.t(d["mask"]), apply_qk_hadamard=True, out_dtype=torch.bfloat16)
+    assert O.rel_fro(o, G.bf16(d["o_mask"])) < 1e-3
