@@ -1,0 +1,470 @@
+#!/usr/bin/env python
+"""Headline benchmark: FP8 GEMM throughput at the LTX-Video DiT linear shapes.
+
+One "step" is one pass of the FP8 GEMM sweep (BASELINE config 2): tokens
+M = 6144*B for B in {1, 4}, (K, N) in {(2048,2048), (2048,6144), (2048,8192),
+(8192,2048)}, each with and without the fused bias + tanh-GELU epilogue, bf16
+output -- 16 launches of the tcgen05 kernel.  Inputs are seeded synthetic
+tensors (activations ~N(0,1) with 0.1 % outlier channels x20 quantised per token,
+weights ~N(0,0.02) per channel), resident in HBM when the timed region starts.
+``value`` is the whole-job FP8 TFLOP/s; ``e2e`` is the same sweep through the
+public ``fp8_linear`` call with pinned HOST activations and results (H2D, fused
+quantizer, GEMM, D2H inside the timed region).
+
+With N > 1 GPUs (one process per GPU under torchrun) each rank runs the sweep on
+its own token shard (sharding by video: no data-path collective); the time is
+the max over ranks, the value the sum of all ranks' FLOPs over that time.
+
+``--impl reference`` times the reference's algorithm on the host CPU cores
+instead (torch-CPU restatement in oracle/, all threads) on a bounded sample of
+the same workload.  ``--full`` adds INT8 GEMM, attention, row-wise kernel and
+DiT-block numbers under ``detail``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+E4M3 = torch.float8_e4m3fn
+SHAPES_KN = [(2048, 2048), (2048, 6144), (2048, 8192), (8192, 2048)]
+BATCHES = [1, 4]
+TOKENS = 6144
+CPU_SAMPLE_ROWS = 1024
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- workload
+def sweep_cases():
+    """(M, K, N, with_bias_gelu) for one step, in launch order."""
+    cases = []
+    for b in BATCHES:
+        for (k, n) in SHAPES_KN:
+            for fused in (False, True):
+                cases.append((TOKENS * b, k, n, fused))
+    return cases
+
+
+def sweep_flops():
+    return sum(2.0 * m * k * n for (m, k, n, _) in sweep_cases())
+
+
+def make_device_operands(dev, kind: str, seed: int):
+    """Quantised operands for every distinct (M,K) activation and (N,K) weight of the sweep.
+    Generated on the device from a seeded generator (the parity tests, not the bench, compare
+    against the CPU oracle), with the distributions of BASELINE config 2."""
+    import q8_kernels_b200 as q8
+    g = torch.Generator(device=dev).manual_seed(seed)
+    qd = E4M3 if kind == "fp8" else torch.int8
+    acts, wts = {}, {}
+    for b in BATCHES:
+        for (k, n) in SHAPES_KN:
+            m = TOKENS * b
+            if (m, k) not in acts:
+                x = torch.randn(m, k, generator=g, device=dev, dtype=torch.float32)
+                idx = torch.randperm(k, generator=g, device=dev)[: max(1, math.ceil(0.001 * k))]
+                x[:, idx] *= 20.0
+                xq, xs = q8.native.tokenwise_quant(x.to(torch.bfloat16), qd)
+                acts[(m, k)] = (xq, xs, x.to(torch.bfloat16))
+                del x
+            if (n, k) not in wts:
+                w = (torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                wq, ws = q8.native.tokenwise_quant(w, qd)
+                bias = torch.randn(n, generator=g, device=dev, dtype=torch.float32) * 0.02
+                wts[(n, k)] = (wq, ws, bias)
+    return acts, wts
+
+
+def run_sweep(q8, acts, wts, kind: str):
+    mm = (q8.native.fp8_mm, q8.native.fp8_mm_bias) if kind == "fp8" else (q8.native.q8_mm, q8.native.q8_mm_bias)
+    launches = 0
+    for (m, k, n, fused) in sweep_cases():
+        xq, xs, _ = acts[(m, k)]
+        wq, ws, bias = wts[(n, k)]
+        if fused:
+            mm[1](xq, wq, bias, xs, ws, True, torch.bfloat16)
+        else:
+            mm[0](xq, wq, xs, ws, False, torch.bfloat16)
+        launches += 1
+    return launches
+
+
+def time_region(fn, steps: int, warmup: int, barrier=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    launches = 0
+    for _ in range(steps):
+        launches += fn() or 0
+    end.record()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    return start.elapsed_time(end), launches
+
+
+def bench_config(world: int, cpu_sample: bool = False):
+    cfg = {"workload": "config2_fp8_gemm_sweep", "tokens": [TOKENS * b for b in BATCHES], "shapes_KN": SHAPES_KN,
+           "epilogues": ["scales", "scales+bias+tanh_gelu"], "out": "bf16", "launches_per_step": len(sweep_cases()),
+           "parallelism": f"dp{world} (by video, no collective)",
+           "l2": "operands + outputs of one step are ~3.7 GB, far beyond the 126 MB L2"}
+    if cpu_sample:
+        cfg["cpu_sample"] = f"each step = first {CPU_SAMPLE_ROWS} token rows of every (K,N) shape, bias+GELU epilogue"
+    return cfg
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_sample_cases():
+    """Bounded sample of the sweep for the CPU: the first 1024 token rows of every (K,N)
+    shape with the fused bias+GELU epilogue (FP8 per-token / per-channel, fp32 accumulate)."""
+    return [(CPU_SAMPLE_ROWS, k, n) for (k, n) in SHAPES_KN]
+
+
+def cpu_run_once(ops):
+    from oracle import q8_oracle as O
+    for (x, wq, ws, bias) in ops:
+        xq, xs = O.tokenwise_quant(x, E4M3)
+        O.fp8_mm(xq, wq, xs, ws, True, torch.bfloat16, bias=bias)
+
+
+def cpu_make_ops(seed=1234):
+    from oracle import q8_oracle as O
+    import helpers as Hp
+    ops = []
+    for i, (m, k, n) in enumerate(cpu_sample_cases()):
+        x = Hp.activations(m, k, seed + i)
+        w = Hp.weights(n, k, seed + 100 + i)
+        wq, ws = O.tokenwise_quant(w, E4M3)
+        ops.append((x, wq, ws, Hp.bias_vec(n, seed + 200 + i)))
+    return ops
+
+
+def cpu_flops():
+    return sum(2.0 * m * k * n for (m, k, n) in cpu_sample_cases())
+
+
+def cpu_baseline(max_seconds: float = 12.0, steps: int = None, warmup: int = 1):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ops = cpu_make_ops()
+    for _ in range(warmup):
+        cpu_run_once(ops)
+    times = []
+    t_all = time.perf_counter()
+    n = 0
+    while True:
+        t0 = time.perf_counter()
+        cpu_run_once(ops)
+        times.append(time.perf_counter() - t0)
+        n += 1
+        if steps is not None:
+            if n >= steps:
+                break
+        elif time.perf_counter() - t_all > max_seconds or n >= 50:
+            break
+    sec = sum(times) / len(times)
+    return {"value": cpu_flops() / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "first 1024 token rows of each (K,N) sweep shape, per-token e4m3 quantizer + fp32 matmul + "
+                      "bias + tanh-GELU (oracle/q8_oracle.py, torch CPU)",
+            "ms_per_step": sec * 1e3, "steps": n}
+
+
+def run_reference_arm(args, rank: int):
+    if rank != 0:
+        return
+    cb = cpu_baseline(steps=max(1, args.steps), warmup=max(1, min(args.warmup, 2)))
+    line = {
+        "impl": "reference", "metric": "fp8_gemm_tflops", "value": cb["value"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": cb["steps"], "warmup": args.warmup, "ms_per_step": cb["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": bench_config(args.gpus, cpu_sample=True),
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- extras (--full)
+def bench_detail(q8, dev, peaks, steps):
+    """INT8 GEMM, attention (configs 3, 4), row-wise kernels and one DiT block; CUDA-event timed."""
+    out = {}
+    nat = q8.native
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / iters
+
+    # per-shape GEMM numbers, both kinds
+    for kind in ("fp8", "int8"):
+        acts, wts = make_device_operands(dev, kind, seed=7)
+        per = {}
+        mm = (nat.fp8_mm, nat.fp8_mm_bias) if kind == "fp8" else (nat.q8_mm, nat.q8_mm_bias)
+        for (m, k, n, fused) in sweep_cases():
+            xq, xs, _ = acts[(m, k)]
+            wq, ws, bias = wts[(n, k)]
+            f = (lambda: mm[1](xq, wq, bias, xs, ws, True, torch.bfloat16)) if fused else \
+                (lambda: mm[0](xq, wq, xs, ws, False, torch.bfloat16))
+            ms = timed(f, max(5, steps))
+            per[f"M{m}_K{k}_N{n}{'_bias_gelu' if fused else ''}"] = round(2.0 * m * k * n / ms / 1e9, 1)
+        out[f"{kind}_gemm_tflops"] = per
+        del acts, wts
+    torch.cuda.empty_cache()
+
+    # attention: config 3 (self, Hadamard fused in the pre-pass) and config 4 (cross, masked)
+    g = torch.Generator(device=dev).manual_seed(3)
+    B, H, S, D = 2, 32, 6144, 64
+    qkv = [torch.randn(B, S, H * D, generator=g, device=dev).to(torch.bfloat16).view(B, S, H, D).transpose(1, 2)
+           for _ in range(3)]
+    F = q8.functional.flash_attention.flash_attn_func
+    q8_, k8_, vt_ = nat.attention_prep(qkv[0], qkv[1], qkv[2], True, math.sqrt(1 / 64) * math.sqrt(64 ** -0.5))
+    ms_core = timed(lambda: nat.flash_attention(q8_, k8_, vt_, 1.0, None, torch.bfloat16), max(5, steps))
+    ms_full = timed(lambda: F(qkv[0], qkv[1], qkv[2], apply_qk_hadamard=True, out_dtype=torch.bfloat16), max(5, steps))
+    fl = 4.0 * B * H * S * S * D
+    out["self_attention"] = {"shape": [B, H, S, D], "kernel_ms": round(ms_core, 4),
+                             "kernel_tflops": round(fl / ms_core / 1e9, 1), "with_prepass_ms": round(ms_full, 4),
+                             "with_prepass_tflops": round(fl / ms_full / 1e9, 1)}
+    kx = [torch.randn(B, 128, H * D, generator=g, device=dev).to(torch.bfloat16).view(B, 128, H, D).transpose(1, 2)
+          for _ in range(2)]
+    lens = torch.tensor([57, 128], dtype=torch.int32, device=dev)
+    q8c, k8c, vtc = nat.attention_prep(qkv[0], kx[0], kx[1], True, math.sqrt(1 / 64) * math.sqrt(64 ** -0.5))
+    ms_x = timed(lambda: nat.flash_attention(q8c, k8c, vtc, 1.0, lens, torch.bfloat16), max(5, steps))
+    bytes_x = B * H * S * D * (1 + 2) + 2 * B * H * 128 * D
+    out["cross_attention"] = {"kernel_ms": round(ms_x, 4), "gbs_fp8_in_bf16_out": round(bytes_x / ms_x / 1e6, 1),
+                              "tflops_dense": round(4.0 * B * H * S * 128 * D / ms_x / 1e9, 1)}
+    del qkv, q8_, k8_, vt_
+    torch.cuda.empty_cache()
+
+    # row-wise kernels: rotate over buffer sets larger than L2
+    rows_list = [(24576, 2048), (24576, 8192)]
+    rw = {}
+    for rows, dim in rows_list:
+        nset = max(2, int(math.ceil(400e6 / (rows * dim * 2))))
+        xs = [torch.randn(rows, dim, generator=g, device=dev).to(torch.bfloat16) for _ in range(nset)]
+        cos = torch.randn(1, rows, dim, generator=g, device=dev)
+        state = {"i": 0}
+
+        def rot():
+            state["i"] = (state["i"] + 1) % nset
+            return xs[state["i"]]
+        hbm = peaks["hbm_gbs"]
+        for name, fn, nbytes in [
+            ("quantizer_int8", lambda: nat.tokenwise_quant(rot(), None), rows * (3 * dim + 4)),
+            ("quantizer_fp8", lambda: nat.tokenwise_quant(rot(), E4M3), rows * (3 * dim + 4)),
+            ("hadamard_bf16", lambda: nat.fast_hadamard_transform(rot(), 1 / math.sqrt(dim), None), rows * 4 * dim),
+            ("hadamard_quant_int8", lambda: nat.hadamard_quant(rot(), 1 / math.sqrt(dim), torch.int8),
+             rows * (3 * dim + 4)),
+            ("rms_norm", lambda: nat.rms_norm(rot(), None, None), rows * (4 * dim + 4)),
+            ("rope_shared_table", lambda: nat.rope(rot().view(1, rows, dim), cos, cos, torch.bfloat16),
+             rows * 12 * dim),
+            ("gelu", lambda: nat.gelu_forward(rot(), None), rows * 4 * dim),
+        ]:
+            ms = timed(fn, 20)
+            gbs = nbytes / ms / 1e6
+            rw[f"{name}_{rows}x{dim}"] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / hbm, 3)}
+        del xs, cos
+        torch.cuda.empty_cache()
+    out["rowwise"] = rw
+    return out
+
+
+# ----------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--full", action="store_true", help="add per-shape, INT8, attention and row-wise numbers")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    args.warmup = max(args.warmup, 3)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import q8_kernels_b200 as q8
+
+    barrier = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        barrier = dist.barrier
+    peaks = load_peaks()
+
+    # ---- device-resident sweep (value)
+    acts, wts = make_device_operands(dev, "fp8", seed=1234 + rank)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms_total, launches = time_region(lambda: run_sweep(q8, acts, wts, "fp8"), args.steps, args.warmup, barrier)
+    clocks = sampler.stop()
+    q8._lib.check_status(dev)
+
+    # ---- end to end through the public API with host buffers
+    pinned_in, pinned_out, weights = {}, {}, {}
+    for (m, k, n, fused) in sweep_cases():
+        if (m, k) not in pinned_in:
+            pinned_in[(m, k)] = acts[(m, k)][2].cpu().pin_memory()
+        pinned_out[(m, n)] = torch.empty(1, m, n, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(pinned_in[(m, k)].numel() * 2 for (m, k, n, f) in sweep_cases())
+    d2h = sum(m * n * 2 for (m, k, n, f) in sweep_cases())
+    fp8_linear = q8.functional.linear.fp8_linear
+
+    def e2e_step():
+        for (m, k, n, fused) in sweep_cases():
+            x = pinned_in[(m, k)].to(dev, non_blocking=True)
+            wq, ws, bias = wts[(n, k)]
+            y = fp8_linear(x, wq, bias if fused else None, None, ws, False, torch.bfloat16)
+            pinned_out[(m, n)].copy_(y, non_blocking=True)
+        return len(sweep_cases()) * 2          # quantizer + GEMM kernel per call
+
+    e2e_steps = max(2, min(args.steps, 5))
+    ms_e2e, _ = time_region(e2e_step, e2e_steps, 1, barrier)
+
+    # ---- reduce over ranks
+    ms_step = ms_total / args.steps
+    ms_e2e_step = ms_e2e / e2e_steps
+    if world > 1:
+        t = torch.tensor([ms_step, ms_e2e_step], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, ms_e2e_step = float(t[0]), float(t[1])
+    flops = sweep_flops()
+    value = world * flops / ms_step / 1e9
+    e2e_value = world * flops / ms_e2e_step / 1e9
+
+    if rank == 0:
+        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        per_gpu = flops / ms_step / 1e9
+        line = {
+            "metric": "fp8_gemm_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": bench_config(world),
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e_step, 3),
+                    "api": "q8_kernels_b200.functional.linear.fp8_linear(bf16 pinned host activations) -> pinned host bf16"},
+            "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": round(peak, 1), "unit": "TFLOP/s",
+                         "frac": round(per_gpu / peak, 4), "traffic": None,
+                         "peak_basis": f"2 x {peaks['_source']} sustained dense bf16 cuBLAS rate "
+                                       f"({peaks['bf16_tflops_sustained']} TFLOP/s); FP8 issues at twice the bf16 rate",
+                         "frac_of_nominal_4500": round(per_gpu / 4500.0, 4),
+                         "kernel": "gemm_8bit_kernel<fp8,BN=256,4 stages>",
+                         "flops_per_launch_avg": flops / len(sweep_cases()),
+                         "avg_launch_ms": round(ms_step / len(sweep_cases()), 5)},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            cb = cpu_baseline()
+            line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"]["value"] = round(cb["value"], 4)
+        if args.full:
+            line["detail"] = bench_detail(q8, dev, peaks, args.steps)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
