@@ -76,7 +76,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -297,7 +297,7 @@ def bench_detail(q8, dev, peaks, steps):
             wq, ws, bias = wts[(n, k)]
             f = (lambda: mm[1](xq, wq, bias, xs, ws, True, torch.bfloat16)) if fused else \
                 (lambda: mm[0](xq, wq, xs, ws, False, torch.bfloat16))
-            ms = timed(f, max(5, steps))
+            ms = timed(f, 20)
             per[f"M{m}_K{k}_N{n}{'_bias_gelu' if fused else ''}"] = round(2.0 * m * k * n / ms / 1e9, 1)
         out[f"{kind}_gemm_tflops"] = per
         del acts, wts
@@ -310,8 +310,8 @@ def bench_detail(q8, dev, peaks, steps):
            for _ in range(3)]
     F = q8.functional.flash_attention.flash_attn_func
     q8_, k8_, vt_ = nat.attention_prep(qkv[0], qkv[1], qkv[2], True, math.sqrt(1 / 64) * math.sqrt(64 ** -0.5))
-    ms_core = timed(lambda: nat.flash_attention(q8_, k8_, vt_, 1.0, None, torch.bfloat16), max(5, steps))
-    ms_full = timed(lambda: F(qkv[0], qkv[1], qkv[2], apply_qk_hadamard=True, out_dtype=torch.bfloat16), max(5, steps))
+    ms_core = timed(lambda: nat.flash_attention(q8_, k8_, vt_, 1.0, None, torch.bfloat16), 10)
+    ms_full = timed(lambda: F(qkv[0], qkv[1], qkv[2], apply_qk_hadamard=True, out_dtype=torch.bfloat16), 10)
     fl = 4.0 * B * H * S * S * D
     out["self_attention"] = {"shape": [B, H, S, D], "kernel_ms": round(ms_core, 4),
                              "kernel_tflops": round(fl / ms_core / 1e9, 1), "with_prepass_ms": round(ms_full, 4),
@@ -320,7 +320,7 @@ def bench_detail(q8, dev, peaks, steps):
           for _ in range(2)]
     lens = torch.tensor([57, 128], dtype=torch.int32, device=dev)
     q8c, k8c, vtc = nat.attention_prep(qkv[0], kx[0], kx[1], True, math.sqrt(1 / 64) * math.sqrt(64 ** -0.5))
-    ms_x = timed(lambda: nat.flash_attention(q8c, k8c, vtc, 1.0, lens, torch.bfloat16), max(5, steps))
+    ms_x = timed(lambda: nat.flash_attention(q8c, k8c, vtc, 1.0, lens, torch.bfloat16), 20)
     bytes_x = B * H * S * D * (1 + 2) + 2 * B * H * 128 * D
     out["cross_attention"] = {"kernel_ms": round(ms_x, 4), "gbs_fp8_in_bf16_out": round(bytes_x / ms_x / 1e6, 1),
                               "tflops_dense": round(4.0 * B * H * S * 128 * D / ms_x / 1e9, 1)}
@@ -364,7 +364,7 @@ def bench_detail(q8, dev, peaks, steps):
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--full", action="store_true", help="add per-shape, INT8, attention and row-wise numbers")

@@ -18,14 +18,15 @@
 //   warp 0      TMA: Q tile once, then K (64 keys x 64 B) and V^T (64 x 64 keys)
 //               tiles, all 64B-swizzled, through KS-deep mbarrier rings
 //   warp 1      TMEM allocation; one thread issues S = Q.K^T (2 x tcgen05.mma
-//               M128 N64 K32) into one of two S buffers (TMEM columns [0,64) and
-//               [64,128)) and O += P.V (2 x M128 N64 K32) into columns [128,192)
-//   warps 2-5   softmax, one thread per query row: tcgen05.ld the scores, max,
-//               rescale O in TMEM when the max moved, exp2, write P as e4m3 into
-//               one of two swizzled shared tiles (the A operand of P.V); at the
-//               end O / l -> bf16 or e4m3 -> global
-// S and P are double buffered, so Q.K^T of block i+1 and P.V of block i-1 run
-// under the softmax of block i; two CTAs share an SM (TMEM 2 x 256 columns).
+//               M128 N64 K32) into one of three S buffers (TMEM columns [0,192))
+//               and O += P.V (2 x M128 N64 K32) into columns [192,256)
+//   warps 2-5   softmax, one thread per query row: the scores of block i are loaded
+//               from TMEM one block ahead (registers double buffered), max, rescale
+//               O in TMEM when the max moved, exp2, write P as e4m3 into one of two
+//               swizzled shared tiles (the A operand of P.V); at the end O / l ->
+//               bf16 or e4m3 -> global
+// S is triple and P double buffered, so Q.K^T of blocks i+1..i+3 and P.V of block
+// i-1 run under the softmax of block i; two CTAs share an SM (TMEM 2 x 256 columns).
 
 #include "common.cuh"
 #include "tcgen05.cuh"
@@ -38,8 +39,9 @@ constexpr int kAttnBM = 128;
 constexpr int kAttnBN = 64;
 constexpr int kAttnKS = 8;                 // K and V ring depth
 constexpr int kAttnThreads = 192;
-constexpr int kAttnTmemCols = 256;         // S0: [0,64), S1: [64,128), O: [128,192)
-constexpr uint32_t kAttnOCol = 128;
+constexpr int kAttnSBufs = 3;              // score buffers in TMEM
+constexpr int kAttnTmemCols = 256;         // S0..S2: [0,192), O: [192,256)
+constexpr uint32_t kAttnOCol = kAttnSBufs * kAttnBN;
 
 struct AttnSmem {
     static constexpr int kQBytes = kAttnBM * kAttnD;               // 8 KB
@@ -51,7 +53,7 @@ struct AttnSmem {
     static constexpr int kVOff = kKOff + kAttnKS * kKBytes;
     static constexpr int kPOff = kVOff + kAttnKS * kVBytes;
     static constexpr int kBarOff = kPOff + 2 * kPBytes;
-    static constexpr int kNumBars = 1 + 4 * kAttnKS + 8;
+    static constexpr int kNumBars = 1 + 4 * kAttnKS + 2 * kAttnSBufs + 4;
     static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemPtrOff + 4;
     static constexpr int kTotal = kAbortOff + 4;
@@ -72,6 +74,27 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// sm_100 packed fp32 pairs (one issue slot for two lanes of FMA-pipe work) and 3-input max
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
 
 __global__ void __launch_bounds__(kAttnThreads, 2)
 flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -87,10 +110,10 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * kAttnKS + s); };
     auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * kAttnKS + s); };
     const uint32_t misc = bar_base + 8u * (1 + 4 * kAttnKS);
-    auto s_full = [&](int b) { return misc + 8u * b; };            // Q.K^T of a block landed in S[b]
-    auto s_free = [&](int b) { return misc + 8u * (2 + b); };      // softmax has read S[b]
-    auto p_full = [&](int b) { return misc + 8u * (4 + b); };      // softmax wrote P[b] (and rescaled O)
-    auto p_free = [&](int b) { return misc + 8u * (6 + b); };      // P.V that read P[b] retired
+    auto s_full = [&](int b) { return misc + 8u * b; };                          // Q.K^T of a block landed in S[b]
+    auto s_free = [&](int b) { return misc + 8u * (kAttnSBufs + b); };           // softmax holds S[b] in registers
+    auto p_full = [&](int b) { return misc + 8u * (2 * kAttnSBufs + b); };       // softmax wrote P[b] (and rescaled O)
+    auto p_free = [&](int b) { return misc + 8u * (2 * kAttnSBufs + 2 + b); };   // P.V that read P[b] retired
     volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
@@ -125,9 +148,11 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             ptx::mbar_init(v_full(s), 1);
             ptx::mbar_init(v_empty(s), 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kAttnSBufs; ++i) {
             ptx::mbar_init(s_full(i), 1);
             ptx::mbar_init(s_free(i), 128);
+        }
+        for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(p_full(i), 128);
             ptx::mbar_init(p_free(i), 1);
         }
@@ -186,12 +211,14 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             const uint32_t o_tmem = tmem_base + kAttnOCol;
             bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
 
-            // S[i % 2] = Q . K(i)^T ; the buffer was last read by the softmax of block i-2
+            // S[i % 3] = Q . K(i)^T ; the buffer was last read by the softmax of block i-3
             auto issue_qk = [&](int i) -> bool {
                 const int s = i % kAttnKS;
-                const int sb = i & 1;
+                const int sb = i % kAttnSBufs;
                 if (!ptx::mbar_wait(k_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_flag)) return false;
-                if (i >= 2 && !ptx::mbar_wait(s_free(sb), (uint32_t)((i - 2) >> 1) & 1u, abort_flag)) return false;
+                if (i >= kAttnSBufs &&
+                    !ptx::mbar_wait(s_free(sb), (uint32_t)((i - kAttnSBufs) / kAttnSBufs) & 1u, abort_flag))
+                    return false;
                 ptx::tcgen05_fence_after_sync();
                 const uint64_t k_desc = ptx::make_kmajor_desc(smem_base + L::kKOff + s * L::kKBytes, 64);
 #pragma unroll
@@ -202,8 +229,7 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 return true;
             };
 
-            if (ok && nblk > 0) ok = issue_qk(0);
-            if (ok && nblk > 1) ok = issue_qk(1);
+            for (int i = 0; ok && i < kAttnSBufs && i < nblk; ++i) ok = issue_qk(i);
             for (int i = 0; ok && i < nblk; ++i) {
                 const int s = i % kAttnKS;
                 const int pb = i & 1;
@@ -217,8 +243,8 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
                 ptx::tcgen05_commit(v_empty(s));
                 ptx::tcgen05_commit(p_free(pb));
-                if (i + 2 < nblk) {
-                    if (!issue_qk(i + 2)) { ok = false; break; }
+                if (i + kAttnSBufs < nblk) {
+                    if (!issue_qk(i + kAttnSBufs)) { ok = false; break; }
                 }
             }
             if (!ok && p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (5 << 8));
@@ -236,40 +262,53 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         float l_run = 0.f;
         bool ok = true;
 
-        for (int i = 0; i < nblk; ++i) {
+        // One 64-key block.  `cur` holds the scores of block i (its TMEM load was issued a step
+        // earlier); the load of block i+1 into `nxt` is issued here and lands while the exps run.
+        auto step = [&](int i, uint32_t (&cur)[2][32], uint32_t (&nxt)[2][32]) -> bool {
             const int jb = nblk - 1 - i;
             const int col0 = jb * kAttnBN;
-            const int buf = i & 1;
-            const uint32_t use_ph = (uint32_t)(i >> 1) & 1u;    // phase of this use of buffer `buf`
+            const int sb = i % kAttnSBufs;
+            const int pb = i & 1;
             const bool need_mask = (col0 + kAttnBN > valid) || (col0 + kAttnBN > p.N);
-            const uint32_t t_s = t_lane + buf * kAttnBN;
-            uint8_t* p_row = smem + L::kPOff + buf * L::kPBytes + r * kAttnBN;
+            uint8_t* p_row = smem + L::kPOff + pb * L::kPBytes + r * kAttnBN;
 
-            if (ok) ok = ptx::mbar_wait(s_full(buf), use_ph, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            ptx::tcgen05_fence_after_sync();
+            __syncwarp();
+            ptx::tmem_wait_ld();                               // scores of block i are in registers
+            ptx::tcgen05_fence_before_sync();
+            ptx::mbar_arrive(s_free(sb));                      // S[sb] may be overwritten by Q.K^T of block i+3
+            if (i + 1 < nblk) {
+                const int nb = (i + 1) % kAttnSBufs;
+                bool got = ptx::mbar_wait(s_full(nb), (uint32_t)((i + 1) / kAttnSBufs) & 1u, abort_flag);
+                if (!__all_sync(0xffffffffu, got)) return false;
+                ptx::tcgen05_fence_after_sync();
+                ptx::tmem_ld_32x32b_x32(t_lane + nb * kAttnBN, nxt[0]);
+                ptx::tmem_ld_32x32b_x32(t_lane + nb * kAttnBN + 32, nxt[1]);
+            }
 
-            // pass 1: row max of the (masked) scores
+            // row max of the (masked) scores; four independent chains of 3-input max
             float m_blk = -INFINITY;
-#pragma unroll 1
-            for (int cc = 0; cc < kAttnBN / 32; ++cc) {
-                uint32_t sr[32];
-                __syncwarp();
-                ptx::tmem_ld_32x32b_x32(t_s + cc * 32, sr);
-                ptx::tmem_wait_ld();
-                if (need_mask) {
+            if (need_mask) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int col = col0 + cc * 32 + j;
-                        float sv = __uint_as_float(sr[j]);
+                        const int col = col0 + h * 32 + j;
+                        float sv = __uint_as_float(cur[h][j]);
                         sv = col >= p.N ? -INFINITY : (col >= valid ? -1.0e6f : sv);
+                        cur[h][j] = __float_as_uint(sv);
                         m_blk = fmaxf(m_blk, sv);
                     }
-                } else {
+            } else {
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) m_blk = fmaxf(m_blk, __uint_as_float(sr[j]));
-                }
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            mx[q] = fmax3(mx[q], __uint_as_float(cur[h][j + 2 * q]), __uint_as_float(cur[h][j + 2 * q + 1]));
+                    }
+                m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             }
             const float m_new = fmaxf(m_run, m_blk);
             const float m_scaled = m_new == -INFINITY ? 0.f : m_new * c;
@@ -277,9 +316,8 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
             if (i > 0 && __any_sync(0xffffffffu, m_new != m_run)) {
                 // O is complete once P.V of the previous block has retired
-                if (ok) ok = ptx::mbar_wait(p_free(buf ^ 1), (uint32_t)((i - 1) >> 1) & 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                bool got = ptx::mbar_wait(p_free(pb ^ 1), (uint32_t)((i - 1) >> 1) & 1u, abort_flag);
+                if (!__all_sync(0xffffffffu, got)) return false;
                 ptx::tcgen05_fence_after_sync();
 #pragma unroll 1
                 for (int h = 0; h < kAttnD / 32; ++h) {
@@ -294,57 +332,86 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 ptx::tmem_wait_st();
             }
             if (i >= 2) {
-                // P[buf] was the A operand of P.V of block i-2
-                if (ok) ok = ptx::mbar_wait(p_free(buf), (uint32_t)((i - 2) >> 1) & 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                // P[pb] was the A operand of P.V of block i-2
+                bool got = ptx::mbar_wait(p_free(pb), (uint32_t)((i - 2) >> 1) & 1u, abort_flag);
+                if (!__all_sync(0xffffffffu, got)) return false;
             }
 
-            // pass 2: p = 2^(s*c - m*c), fp32 row sum, e4m3 P into the swizzled smem tile
+            // p = 2^(s*c - m*c), fp32 row sum, e4m3 P into the swizzled smem tile
             float row_sum = 0.f;
-#pragma unroll 1
-            for (int cc = 0; cc < kAttnBN / 32; ++cc) {
-                uint32_t sr[32];
-                __syncwarp();
-                ptx::tmem_ld_32x32b_x32(t_s + cc * 32, sr);
-                ptx::tmem_wait_ld();
-                if (cc == kAttnBN / 32 - 1) {                  // S[buf] fully consumed: Q.K^T of block i+2 may overwrite it
-                    ptx::tcgen05_fence_before_sync();
-                    ptx::mbar_arrive(s_free(buf));
-                }
-                float pv[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float sv = __uint_as_float(sr[j]);
-                    if (need_mask) {
-                        const int col = col0 + cc * 32 + j;
-                        sv = col >= p.N ? -INFINITY : (col >= valid ? -1.0e6f : sv);
-                    }
-                    // Masked scores are -1e6: there the product must be rounded before the subtraction
-                    // (as the unfused reference arithmetic does), or the fma's exact product leaves a
-                    // residual of up to half an ulp of 1.4e6 in the exponent.
-                    const float e = need_mask ? __fsub_rn(__fmul_rn(sv, c), m_scaled) : fmaf(sv, c, -m_scaled);
-                    pv[j] = fast_exp2(e);
-                    row_sum += pv[j];
-                }
+            if (need_mask) {
+                // Masked scores are -1e6: there the product must be rounded before the subtraction
+                // (as the unfused reference arithmetic does), or the fma's exact product leaves a
+                // residual of up to half an ulp of 1.4e6 in the exponent.
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    uint32_t w[4];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int j = h * 16 + q * 4;
-                        w[q] = (uint32_t)float2_to_e4m3x2_sat(pv[j], pv[j + 1]) |
-                               ((uint32_t)float2_to_e4m3x2_sat(pv[j + 2], pv[j + 3]) << 16);
+                    for (int g = 0; g < 2; ++g) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            float pv[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float sv = __uint_as_float(cur[h][g * 16 + q * 4 + e]);
+                                pv[e] = fast_exp2(__fsub_rn(__fmul_rn(sv, c), m_scaled));
+                                row_sum += pv[e];
+                            }
+                            w[q] = (uint32_t)float2_to_e4m3x2_sat(pv[0], pv[1]) |
+                                   ((uint32_t)float2_to_e4m3x2_sat(pv[2], pv[3]) << 16);
+                        }
+                        const uint32_t chunk = (uint32_t)(h * 2 + g) ^ swz;
+                        *reinterpret_cast<uint4*>(p_row + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    const uint32_t chunk = (uint32_t)(cc * 2 + h) ^ swz;
-                    *reinterpret_cast<uint4*>(p_row + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+            } else {
+                const float2 c2 = make_float2(c, c);
+                const float2 nm2 = make_float2(-m_scaled, -m_scaled);
+                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int j = g * 16 + q * 4;
+                            const float2 e0 = ffma2(make_float2(__uint_as_float(cur[h][j]), __uint_as_float(cur[h][j + 1])), c2, nm2);
+                            const float2 e1 = ffma2(make_float2(__uint_as_float(cur[h][j + 2]), __uint_as_float(cur[h][j + 3])), c2, nm2);
+                            const float2 p0 = make_float2(fast_exp2(e0.x), fast_exp2(e0.y));
+                            const float2 p1 = make_float2(fast_exp2(e1.x), fast_exp2(e1.y));
+                            sum_a = fadd2(sum_a, p0);
+                            sum_b = fadd2(sum_b, p1);
+                            w[q] = (uint32_t)float2_to_e4m3x2_sat(p0.x, p0.y) |
+                                   ((uint32_t)float2_to_e4m3x2_sat(p1.x, p1.y) << 16);
+                        }
+                        const uint32_t chunk = (uint32_t)(h * 2 + g) ^ swz;
+                        *reinterpret_cast<uint4*>(p_row + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+                row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
             }
             l_run = l_run * alpha + row_sum;
             m_run = m_new;
             ptx::fence_proxy_async_smem();                     // P visible to the tensor core's smem reads
             ptx::tcgen05_fence_before_sync();                  // orders the O rescale before the signal
-            ptx::mbar_arrive(p_full(buf));
+            ptx::mbar_arrive(p_full(pb));
+            return true;
+        };
+
+        uint32_t s_a[2][32], s_b[2][32];
+        if (nblk > 0) {
+            ok = ptx::mbar_wait(s_full(0), 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                ptx::tcgen05_fence_after_sync();
+                ptx::tmem_ld_32x32b_x32(t_lane, s_a[0]);
+                ptx::tmem_ld_32x32b_x32(t_lane + 32, s_a[1]);
+            }
+        }
+        for (int i = 0; ok && i < nblk; i += 2) {
+            ok = step(i, s_a, s_b);
+            if (ok && i + 1 < nblk) ok = step(i + 1, s_b, s_a);
         }
 
         // epilogue: O / l

@@ -4,14 +4,15 @@
 //   A [bs_a, M, K], B [bs_b, N, K]  int8 (kind::i8, int32 accumulate) or
 //   e4m3 (kind::f8f6f4, fp32 accumulate), both K-contiguous.
 //
-// Structure (one persistent CTA per SM, 6 warps):
+// Structure (one persistent CTA per SM, 10 warps):
 //   warp 0      TMA producer: 128 x 128-byte A tile and BN x 128-byte B tile per
 //               stage into 128B-swizzled shared memory, STAGES-deep mbarrier ring
 //   warp 1      allocates TMEM; one thread issues tcgen05.mma (M=128, N=BN, K=32),
 //               4 per stage, accumulating into one of two TMEM buffers
-//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (thread = row),
-//               scale, bias, GELU, cast, 16-byte global stores; runs while the
-//               MMA warp fills the other TMEM buffer with the next tile
+//   warps 2-9   epilogue: tcgen05.ld the finished accumulator (thread = one row of
+//               one half of the columns, next chunk's load in flight), scale, bias,
+//               GELU, cast, 16-byte global stores; runs while the MMA warp fills
+//               the other TMEM buffer with the next tile
 // Tiles are assigned statically: tile = blockIdx.x + i * gridDim.x, N fastest.
 //
 // Epilogue arithmetic follows csrc/gemm/q8_matmul_bias.cu:29-33,315-371 of the
@@ -26,7 +27,8 @@ namespace q8k {
 
 constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 128;          // bytes == elements along K per stage
-constexpr int kGemmThreads = 192;
+constexpr int kGemmEpilogueThreads = 256;
+constexpr int kGemmThreads = 64 + kGemmEpilogueThreads;
 
 struct GemmParams {
     const float* a_scales;
@@ -37,8 +39,6 @@ struct GemmParams {
     int M, N, K;
     int batch_a, batch_b;             // 1 when that operand carries a batch dim
     int m_tiles, n_tiles, total_tiles;
-    int out_e4m3;
-    int fuse_gelu;
 };
 
 template <int BN, int STAGES>
@@ -66,7 +66,7 @@ __device__ __forceinline__ float gelu_tanh_fast(float y) {
     return 0.5f * y * (1.0f + t);
 }
 
-template <bool INT8, int BN, int STAGES>
+template <bool INT8, int BN, int STAGES, bool GELU, bool OUT_E4M3>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
@@ -105,7 +105,7 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(tmem_full_bar(a), 1);
-            ptx::mbar_init(tmem_empty_bar(a), 128);
+            ptx::mbar_init(tmem_empty_bar(a), kGemmEpilogueThreads);
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -189,9 +189,14 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!ok && p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (2 << 8));
         }
     } else {
-        // ------------------------------------------------ epilogue (warps 2..5, 128 threads)
-        const int quarter = warp & 3;                          // TMEM lanes [32*quarter, +32) belong to this warp
+        // ------------------------------------------------ epilogue (warps 2..9, 256 threads)
+        // Warp w may touch TMEM lanes [32*(w%4), +32).  Warps 2-5 take the left half of the
+        // tile's columns, warps 6-9 the right half; a thread owns one output row of its half.
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int epi_tid = threadIdx.x - 64;
+        constexpr int HALF_COLS = BN / 2;
+        constexpr int NCH = HALF_COLS / 32;                    // 32-column chunks per thread and tile
         uint32_t tile_i = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++tile_i) {
@@ -202,14 +207,14 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t acc = tile_i & 1u;
             const uint32_t acc_ph = (tile_i >> 1) & 1u;
 
-            asm volatile("bar.sync 1, 128;" ::: "memory");     // everyone is done with the previous tile's column data
-            for (int c = epi_tid; c < BN; c += 128) {
+            asm volatile("bar.sync 1, 256;" ::: "memory");     // everyone is done with the previous tile's column data
+            for (int c = epi_tid; c < BN; c += kGemmEpilogueThreads) {
                 const int n = n0 + c;
                 const bool in = n < p.N;
                 col_scale_smem[c] = in ? p.b_scales[(p.batch_b ? (int64_t)batch * p.N : 0) + n] : 0.f;
                 bias_smem[c] = (in && p.bias != nullptr) ? p.bias[n] : 0.f;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
 
             if (ok) ok = ptx::mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag);
             ok = __all_sync(0xffffffffu, ok);                  // keep the warp convergent for tcgen05.ld
@@ -220,59 +225,64 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const bool row_ok = row < p.M;
             const float sa = row_ok ? p.a_scales[(p.batch_a ? (int64_t)batch * p.M : 0) + row] : 0.f;
             const int64_t out_row = ((int64_t)batch * p.M + row) * p.N;
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+            const int col_base = half * HALF_COLS;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + col_base;
 
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                __syncwarp();                                  // tcgen05.ld is warp-collective
-                ptx::tmem_ld_32x32b_x32(t_row + c * 32, r);
-                ptx::tmem_wait_ld();
-                const int nc = n0 + c * 32;
-                if (row_ok && nc < p.N) {
-                float y[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float accf = INT8 ? (float)(int)r[j] : __uint_as_float(r[j]);
-                    float v = fmaf(accf, sa * col_scale_smem[c * 32 + j], bias_smem[c * 32 + j]);
-                    if (p.fuse_gelu) v = gelu_tanh_fast(v);
-                    y[j] = v;
-                }
-                const int valid = min(32, p.N - nc);           // N % 16 == 0, so valid is 16 or 32
-                if (p.out_e4m3) {
-                    uint8_t* o = reinterpret_cast<uint8_t*>(p.out) + out_row + nc;
-#pragma unroll
-                    for (int v4 = 0; v4 < 2; ++v4) {
-                        if (v4 * 16 < valid) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int j = v4 * 16 + q * 4;
-                                w[q] = (uint32_t)float2_to_e4m3x2_sat(y[j], y[j + 1]) |
-                                       ((uint32_t)float2_to_e4m3x2_sat(y[j + 2], y[j + 3]) << 16);
-                            }
-                            reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    }
-                } else {
-                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + out_row + nc;
-#pragma unroll
-                    for (int v4 = 0; v4 < 4; ++v4) {
-                        if (v4 * 8 < valid) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int j = v4 * 8 + q * 2;
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(y[j], y[j + 1]);
-                                w[q] = *reinterpret_cast<uint32_t*>(&b2);
-                            }
-                            reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    }
-                }
-                }
-            }
+            // The load of chunk c+1 is in flight while chunk c is scaled, activated and stored.
+            uint32_t r[2][32];
             __syncwarp();
+            ptx::tmem_ld_32x32b_x32(t_row, r[0]);
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                ptx::tmem_wait_ld();
+                if (c + 1 < NCH) ptx::tmem_ld_32x32b_x32(t_row + (c + 1) * 32, r[(c + 1) & 1]);
+                const int cl = col_base + c * 32;              // column inside the tile
+                const int nc = n0 + cl;
+                if (row_ok && nc < p.N) {
+                    const uint32_t(&rc)[32] = r[c & 1];
+                    float y[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float accf = INT8 ? (float)(int)rc[j] : __uint_as_float(rc[j]);
+                        float v = fmaf(accf, sa * col_scale_smem[cl + j], bias_smem[cl + j]);
+                        if constexpr (GELU) v = gelu_tanh_fast(v);
+                        y[j] = v;
+                    }
+                    const int valid = min(32, p.N - nc);       // N % 16 == 0, so valid is 16 or 32
+                    if constexpr (OUT_E4M3) {
+                        uint8_t* o = reinterpret_cast<uint8_t*>(p.out) + out_row + nc;
+#pragma unroll
+                        for (int v4 = 0; v4 < 2; ++v4) {
+                            if (v4 * 16 < valid) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const int j = v4 * 16 + q * 4;
+                                    w[q] = (uint32_t)float2_to_e4m3x2_sat(y[j], y[j + 1]) |
+                                           ((uint32_t)float2_to_e4m3x2_sat(y[j + 2], y[j + 3]) << 16);
+                                }
+                                reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    } else {
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + out_row + nc;
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4) {
+                            if (v4 * 8 < valid) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const int j = v4 * 8 + q * 2;
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(y[j], y[j + 1]);
+                                    w[q] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
+                                reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();                                  // reconverge before the next warp-collective TMEM op
+            }
             ptx::tcgen05_fence_before_sync();
             ptx::mbar_arrive(tmem_empty_bar(acc));
         }
@@ -302,10 +312,10 @@ static int num_sms() {
     return g_num_sms;
 }
 
-template <bool INT8, int BN, int STAGES>
+template <bool INT8, int BN, int STAGES, bool GELU, bool OUT_E4M3>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
     using L = GemmSmem<BN, STAGES>;
-    auto kern = gemm_8bit_kernel<INT8, BN, STAGES>;
+    auto kern = gemm_8bit_kernel<INT8, BN, STAGES, GELU, OUT_E4M3>;
     Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
     const int grid = p.total_tiles < num_sms() ? p.total_tiles : num_sms();
     kern<<<grid, kGemmThreads, L::kDynamic, st>>>(ta, tb, p);
@@ -361,12 +371,23 @@ static int gemm_8bit(bool int8, const void* a, const void* b, const float* bias,
     const int64_t total = (int64_t)p.m_tiles * p.n_tiles * batch;
     Q8K_REQUIRE(total <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many tiles", op);
     p.total_tiles = (int)total;
-    p.out_e4m3 = out_dtype == Q8K_DT_E4M3;
-    p.fuse_gelu = fuse_gelu != 0;
-
     cudaStream_t st = (cudaStream_t)stream;
-    if (int8) return bn256 ? launch_gemm<true, 256, 4>(ta, tb, p, st) : launch_gemm<true, 128, 6>(ta, tb, p, st);
-    return bn256 ? launch_gemm<false, 256, 4>(ta, tb, p, st) : launch_gemm<false, 128, 6>(ta, tb, p, st);
+    const bool gelu = fuse_gelu != 0;
+    const bool e4m3 = out_dtype == Q8K_DT_E4M3;
+#define Q8K_GEMM_DISPATCH(I8, BNV, ST)                                                        \
+    do {                                                                                      \
+        if (gelu) return e4m3 ? launch_gemm<I8, BNV, ST, true, true>(ta, tb, p, st)           \
+                              : launch_gemm<I8, BNV, ST, true, false>(ta, tb, p, st);         \
+        return e4m3 ? launch_gemm<I8, BNV, ST, false, true>(ta, tb, p, st)                    \
+                    : launch_gemm<I8, BNV, ST, false, false>(ta, tb, p, st);                  \
+    } while (0)
+    if (int8) {
+        if (bn256) Q8K_GEMM_DISPATCH(true, 256, 4);
+        Q8K_GEMM_DISPATCH(true, 128, 6);
+    }
+    if (bn256) Q8K_GEMM_DISPATCH(false, 256, 4);
+    Q8K_GEMM_DISPATCH(false, 128, 6);
+#undef Q8K_GEMM_DISPATCH
 }
 
 }  // namespace q8k
