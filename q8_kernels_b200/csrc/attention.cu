@@ -14,19 +14,23 @@
 // block's rescale) except for key_lens[b] == 0, where every block is processed
 // and the result is the mean of V, as in the reference.
 //
-// Structure: one CTA per 128 query rows of one (batch, head); 6 warps.
+// Structure: one CTA per 128 query rows of one (batch, head), two warpgroups
+// whose register budgets are rebalanced with setmaxnreg (24 / 104 per thread).
 //   warp 0      TMA: Q tile once, then K (64 keys x 64 B) and V^T (64 x 64 keys)
 //               tiles, all 64B-swizzled, through KS-deep mbarrier rings
 //   warp 1      TMEM allocation; one thread issues S = Q.K^T (2 x tcgen05.mma
-//               M128 N64 K32) into one of three S buffers (TMEM columns [0,192))
-//               and O += P.V (2 x M128 N64 K32) into columns [192,256)
-//   warps 2-5   softmax, one thread per query row: the scores of block i are loaded
-//               from TMEM one block ahead (registers double buffered), max, rescale
-//               O in TMEM when the max moved, exp2, write P as e4m3 into one of two
-//               swizzled shared tiles (the A operand of P.V); at the end O / l ->
-//               bf16 or e4m3 -> global
-// S is triple and P double buffered, so Q.K^T of blocks i+1..i+3 and P.V of block
-// i-1 run under the softmax of block i; two CTAs share an SM (TMEM 2 x 256 columns).
+//               M128 N64 K32) into TMEM columns [0,64) and O += P.V (2 x M128 N64
+//               K32) into columns [64,128)
+//   warps 4-7   softmax, one thread per query row: the scores of block i sit in
+//               registers (each half is refilled from TMEM with block i+1 as soon
+//               as its exps are done, which also frees S for the next Q.K^T), max,
+//               O *= alpha in TMEM when a row max of the warp moved, exp2, P as
+//               e4m3 into one of two swizzled shared tiles (the A operand of
+//               P.V); at the end O / l -> bf16 or e4m3 -> global
+// The softmax chain of one CTA is latency bound (barrier hand-offs, TMEM round
+// trips), so the kernel is sized for FOUR resident CTAs per SM -- 128 TMEM
+// columns, 64 registers per thread at launch, ~50 KB shared memory -- and lets
+// the warp schedulers interleave them to keep the exp2 unit busy.
 
 #include "common.cuh"
 #include "tcgen05.cuh"
@@ -37,11 +41,13 @@ namespace q8k {
 constexpr int kAttnD = 64;
 constexpr int kAttnBM = 128;
 constexpr int kAttnBN = 64;
-constexpr int kAttnKS = 8;                 // K and V ring depth
-constexpr int kAttnThreads = 192;
-constexpr int kAttnSBufs = 3;              // score buffers in TMEM
-constexpr int kAttnTmemCols = 256;         // S0..S2: [0,192), O: [192,256)
-constexpr uint32_t kAttnOCol = kAttnSBufs * kAttnBN;
+constexpr int kAttnKS = 3;                   // K and V ring depth
+constexpr int kAttnThreads = 256;            // warpgroup 0: TMA + MMA, warpgroup 1: softmax
+constexpr int kAttnRegsLaunch = 64;          // registers per thread at launch: 4 CTAs x 256 threads x 64 = 65536
+constexpr int kAttnRegsIo = 24;              // after setmaxnreg: TMA / MMA warpgroup
+constexpr int kAttnRegsSoftmax = 104;        //                    softmax warpgroup (2 * 64 = 24 + 104)
+constexpr int kAttnTmemCols = 128;           // S: [0,64), O: [64,128)
+constexpr uint32_t kAttnOCol = kAttnBN;
 
 struct AttnSmem {
     static constexpr int kQBytes = kAttnBM * kAttnD;               // 8 KB
@@ -53,7 +59,7 @@ struct AttnSmem {
     static constexpr int kVOff = kKOff + kAttnKS * kKBytes;
     static constexpr int kPOff = kVOff + kAttnKS * kVBytes;
     static constexpr int kBarOff = kPOff + 2 * kPBytes;
-    static constexpr int kNumBars = 1 + 4 * kAttnKS + 2 * kAttnSBufs + 4;
+    static constexpr int kNumBars = 1 + 4 * kAttnKS + 5;
     static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemPtrOff + 4;
     static constexpr int kTotal = kAbortOff + 4;
@@ -73,6 +79,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+template <int N> __device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+// One arrival per warp: every lane has done its own fences, the warp converges, lane 0 signals.
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(bar);
 }
 // sm_100 packed fp32 pairs (one issue slot for two lanes of FMA-pipe work) and 3-input max
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
@@ -95,8 +112,21 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
         : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
     return *reinterpret_cast<float2*>(&d);
 }
+// four fp32 -> four e4m3 (saturating) packed in one word, lowest byte first
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+    uint32_t r;
+    asm("{\n\t"
+        ".reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t"
+        "}"
+        : "=r"(r)
+        : "f"(a), "f"(b), "f"(c), "f"(d));
+    return r;
+}
 
-__global__ void __launch_bounds__(kAttnThreads, 2)
+__global__ void __maxnreg__(kAttnRegsLaunch)
 flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
     using L = AttnSmem;
@@ -110,10 +140,10 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * kAttnKS + s); };
     auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * kAttnKS + s); };
     const uint32_t misc = bar_base + 8u * (1 + 4 * kAttnKS);
-    auto s_full = [&](int b) { return misc + 8u * b; };                          // Q.K^T of a block landed in S[b]
-    auto s_free = [&](int b) { return misc + 8u * (kAttnSBufs + b); };           // softmax holds S[b] in registers
-    auto p_full = [&](int b) { return misc + 8u * (2 * kAttnSBufs + b); };       // softmax wrote P[b] (and rescaled O)
-    auto p_free = [&](int b) { return misc + 8u * (2 * kAttnSBufs + 2 + b); };   // P.V that read P[b] retired
+    const uint32_t s_full = misc;                                // Q.K^T of block i landed in S        (phase i)
+    const uint32_t s_free = misc + 8u;                           // softmax holds block i in registers  (phase i)
+    auto p_full = [&](int b) { return misc + 8u * (2 + b); };    // softmax wrote P[b], O is rescaled   (phase i/2)
+    const uint32_t pv_done = misc + 32u;                         // P.V of block i retired              (phase i)
     volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
@@ -148,14 +178,11 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             ptx::mbar_init(v_full(s), 1);
             ptx::mbar_init(v_empty(s), 1);
         }
-        for (int i = 0; i < kAttnSBufs; ++i) {
-            ptx::mbar_init(s_full(i), 1);
-            ptx::mbar_init(s_free(i), 128);
-        }
-        for (int i = 0; i < 2; ++i) {
-            ptx::mbar_init(p_full(i), 128);
-            ptx::mbar_init(p_free(i), 1);
-        }
+        ptx::mbar_init(s_full, 1);
+        ptx::mbar_init(s_free, 4);                             // one arrival per softmax warp
+        ptx::mbar_init(p_full(0), 4);
+        ptx::mbar_init(p_full(1), 4);
+        ptx::mbar_init(pv_done, 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
@@ -172,85 +199,100 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     ptx::tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
-    if (warp == 0) {
-        // ------------------------------------------------ TMA producer
-        if (lane == 0) {
-            bool ok = true;
-            ptx::mbar_arrive_expect_tx(q_full, L::kQBytes);
-            ptx::tma_load_3d(smem_base + L::kQOff, &tmap_q, q_full, 0, m0, bh);
-            int issued = 0;
-            for (int i = 0; ok && i < nblk; ++i) {
-                const int jb = nblk - 1 - i;
-                const int s = i % kAttnKS;
-                const uint32_t ph = (i / kAttnKS) & 1u;
-                if (!ptx::mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
-                ptx::mbar_arrive_expect_tx(k_full(s), L::kKBytes);
-                ptx::tma_load_3d(smem_base + L::kKOff + s * L::kKBytes, &tmap_k, k_full(s), 0, jb * kAttnBN, bh);
-                if (!ptx::mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
-                ptx::mbar_arrive_expect_tx(v_full(s), L::kVBytes);
-                ptx::tma_load_3d(smem_base + L::kVOff + s * L::kVBytes, &tmap_v, v_full(s), jb * kAttnBN, 0, bh);
-                issued = i + 1;
-            }
-            if (!ok) {
-                if (p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (4 << 8));
-                // bounded grace period for copies still in flight
-                const int first = issued > kAttnKS ? issued - kAttnKS : 0;
-                for (int i = first; i < issued; ++i) {
-                    const unsigned long long t0 = ptx::globaltimer_ns();
-                    while (!(ptx::mbar_try_wait(k_full(i % kAttnKS), (i / kAttnKS) & 1u) &&
-                             ptx::mbar_try_wait(v_full(i % kAttnKS), (i / kAttnKS) & 1u)) &&
-                           ptx::globaltimer_ns() - t0 < 100000000ull) {}
+    // Each warpgroup runs in a branch of its own that starts with its register re-budgeting and
+    // ends with the CTA-wide teardown barrier, so no code path mixes two budgets.
+    auto teardown_barrier = [&]() {
+        ptx::tcgen05_fence_before_sync();
+        asm volatile("bar.sync 0, %0;" ::"n"(kAttnThreads) : "memory");
+    };
+    if (warp < 4) {
+        reg_dealloc<kAttnRegsIo>();
+        if (warp == 0) {
+            // -------------------------------------------- TMA producer
+            if (lane == 0) {
+                bool ok = true;
+                ptx::mbar_arrive_expect_tx(q_full, L::kQBytes);
+                ptx::tma_load_3d(smem_base + L::kQOff, &tmap_q, q_full, 0, m0, bh);
+                int issued = 0;
+                for (int i = 0; ok && i < nblk; ++i) {
+                    const int jb = nblk - 1 - i;
+                    const int s = i % kAttnKS;
+                    const uint32_t ph = (i / kAttnKS) & 1u;
+                    if (!ptx::mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(k_full(s), L::kKBytes);
+                    ptx::tma_load_3d(smem_base + L::kKOff + s * L::kKBytes, &tmap_k, k_full(s), 0, jb * kAttnBN, bh);
+                    if (!ptx::mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(v_full(s), L::kVBytes);
+                    ptx::tma_load_3d(smem_base + L::kVOff + s * L::kVBytes, &tmap_v, v_full(s), jb * kAttnBN, 0, bh);
+                    issued = i + 1;
                 }
+                if (!ok) {
+                    if (p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (4 << 8));
+                    // bounded grace period for copies still in flight
+                    const int first = issued > kAttnKS ? issued - kAttnKS : 0;
+                    for (int i = first; i < issued; ++i) {
+                        const unsigned long long t0 = ptx::globaltimer_ns();
+                        while (!(ptx::mbar_try_wait(k_full(i % kAttnKS), (i / kAttnKS) & 1u) &&
+                                 ptx::mbar_try_wait(v_full(i % kAttnKS), (i / kAttnKS) & 1u)) &&
+                               ptx::globaltimer_ns() - t0 < 100000000ull) {}
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // -------------------------------------------- MMA issuer
+            if (lane == 0) {
+                constexpr uint32_t IDESC = ptx::make_idesc_e4m3(kAttnBM, kAttnBN);   // both GEMMs are M128 N64
+                const uint64_t q_desc = ptx::make_kmajor_desc(smem_base + L::kQOff, 64);
+                const uint32_t s_tmem = tmem_base;
+                const uint32_t o_tmem = tmem_base + kAttnOCol;
+                bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
+
+                // S = Q . K(i)^T ; S is free once the softmax warps hold block i-1 in registers
+                auto issue_qk = [&](int i) -> bool {
+                    const int s = i % kAttnKS;
+                    if (!ptx::mbar_wait(k_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_flag)) return false;
+                    if (i >= 1 && !ptx::mbar_wait(s_free, (uint32_t)(i - 1) & 1u, abort_flag)) return false;
+                    ptx::tcgen05_fence_after_sync();
+                    const uint64_t k_desc = ptx::make_kmajor_desc(smem_base + L::kKOff + s * L::kKBytes, 64);
+#pragma unroll
+                    for (int k = 0; k < kAttnD / 32; ++k)
+                        ptx::mma_f8f6f4(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC, k > 0 ? 1u : 0u);
+                    ptx::tcgen05_commit(k_empty(s));
+                    ptx::tcgen05_commit(s_full);
+                    return true;
+                };
+
+                if (ok && nblk > 0) ok = issue_qk(0);
+                for (int i = 0; ok && i < nblk; ++i) {
+                    // scores of the next block first: the softmax warps refill from them mid-step
+                    if (i + 1 < nblk) {
+                        if (!issue_qk(i + 1)) { ok = false; break; }
+                    }
+                    const int s = i % kAttnKS;
+                    const int pb = i & 1;
+                    if (!ptx::mbar_wait(v_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait(p_full(pb), (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
+                    ptx::tcgen05_fence_after_sync();
+                    const uint64_t p_desc = ptx::make_kmajor_desc(smem_base + L::kPOff + pb * L::kPBytes, 64);
+                    const uint64_t v_desc = ptx::make_kmajor_desc(smem_base + L::kVOff + s * L::kVBytes, 64);
+#pragma unroll
+                    for (int k = 0; k < kAttnBN / 32; ++k)
+                        ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+                    ptx::tcgen05_commit(v_empty(s));
+                    ptx::tcgen05_commit(pv_done);
+                }
+                if (!ok && p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (5 << 8));
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t IDESC = ptx::make_idesc_e4m3(kAttnBM, kAttnBN);   // both GEMMs are M128 N64
-            const uint64_t q_desc = ptx::make_kmajor_desc(smem_base + L::kQOff, 64);
-            const uint32_t o_tmem = tmem_base + kAttnOCol;
-            bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
-
-            // S[i % 3] = Q . K(i)^T ; the buffer was last read by the softmax of block i-3
-            auto issue_qk = [&](int i) -> bool {
-                const int s = i % kAttnKS;
-                const int sb = i % kAttnSBufs;
-                if (!ptx::mbar_wait(k_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_flag)) return false;
-                if (i >= kAttnSBufs &&
-                    !ptx::mbar_wait(s_free(sb), (uint32_t)((i - kAttnSBufs) / kAttnSBufs) & 1u, abort_flag))
-                    return false;
-                ptx::tcgen05_fence_after_sync();
-                const uint64_t k_desc = ptx::make_kmajor_desc(smem_base + L::kKOff + s * L::kKBytes, 64);
-#pragma unroll
-                for (int k = 0; k < kAttnD / 32; ++k)
-                    ptx::mma_f8f6f4(tmem_base + sb * kAttnBN, q_desc + 2 * k, k_desc + 2 * k, IDESC, k > 0 ? 1u : 0u);
-                ptx::tcgen05_commit(k_empty(s));
-                ptx::tcgen05_commit(s_full(sb));
-                return true;
-            };
-
-            for (int i = 0; ok && i < kAttnSBufs && i < nblk; ++i) ok = issue_qk(i);
-            for (int i = 0; ok && i < nblk; ++i) {
-                const int s = i % kAttnKS;
-                const int pb = i & 1;
-                if (!ptx::mbar_wait(v_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_flag)) { ok = false; break; }
-                if (!ptx::mbar_wait(p_full(pb), (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
-                ptx::tcgen05_fence_after_sync();
-                const uint64_t p_desc = ptx::make_kmajor_desc(smem_base + L::kPOff + pb * L::kPBytes, 64);
-                const uint64_t v_desc = ptx::make_kmajor_desc(smem_base + L::kVOff + s * L::kVBytes, 64);
-#pragma unroll
-                for (int k = 0; k < kAttnBN / 32; ++k)
-                    ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
-                ptx::tcgen05_commit(v_empty(s));
-                ptx::tcgen05_commit(p_free(pb));
-                if (i + kAttnSBufs < nblk) {
-                    if (!issue_qk(i + kAttnSBufs)) { ok = false; break; }
-                }
-            }
-            if (!ok && p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (5 << 8));
+        teardown_barrier();
+        if (warp == 1) {
+            __syncwarp();
+            ptx::tcgen05_fence_after_sync();
+            ptx::tmem_dealloc<kAttnTmemCols>(tmem_base);
         }
     } else {
-        // ------------------------------------------------ softmax / correction / epilogue
+        reg_alloc<kAttnRegsSoftmax>();
+        // ------------------------------------------------ softmax / O rescale / epilogue
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                      // row of the tile == TMEM lane
         const int row = m0 + r;
@@ -261,29 +303,29 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         float m_run = -INFINITY;
         float l_run = 0.f;
         bool ok = true;
+        uint32_t cur[2][32];                                    // scores of the block being processed
 
-        // One 64-key block.  `cur` holds the scores of block i (its TMEM load was issued a step
-        // earlier); the load of block i+1 into `nxt` is issued here and lands while the exps run.
-        auto step = [&](int i, uint32_t (&cur)[2][32], uint32_t (&nxt)[2][32]) -> bool {
+        if (nblk > 0) {
+            ok = ptx::mbar_wait(s_full, 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                ptx::tcgen05_fence_after_sync();
+                ptx::tmem_ld_32x32b_x32(t_lane, cur[0]);
+                ptx::tmem_ld_32x32b_x32(t_lane + 32, cur[1]);
+                ptx::tmem_wait_ld();
+                ptx::tcgen05_fence_before_sync();
+                warp_arrive(s_free, lane);                      // Q.K^T of block 1 may overwrite S
+            }
+        }
+
+#pragma unroll 1
+        for (int i = 0; ok && i < nblk; ++i) {
             const int jb = nblk - 1 - i;
             const int col0 = jb * kAttnBN;
-            const int sb = i % kAttnSBufs;
             const int pb = i & 1;
             const bool need_mask = (col0 + kAttnBN > valid) || (col0 + kAttnBN > p.N);
+            const bool prefetch = i + 1 < nblk;
             uint8_t* p_row = smem + L::kPOff + pb * L::kPBytes + r * kAttnBN;
-
-            __syncwarp();
-            ptx::tmem_wait_ld();                               // scores of block i are in registers
-            ptx::tcgen05_fence_before_sync();
-            ptx::mbar_arrive(s_free(sb));                      // S[sb] may be overwritten by Q.K^T of block i+3
-            if (i + 1 < nblk) {
-                const int nb = (i + 1) % kAttnSBufs;
-                bool got = ptx::mbar_wait(s_full(nb), (uint32_t)((i + 1) / kAttnSBufs) & 1u, abort_flag);
-                if (!__all_sync(0xffffffffu, got)) return false;
-                ptx::tcgen05_fence_after_sync();
-                ptx::tmem_ld_32x32b_x32(t_lane + nb * kAttnBN, nxt[0]);
-                ptx::tmem_ld_32x32b_x32(t_lane + nb * kAttnBN + 32, nxt[1]);
-            }
 
             // row max of the (masked) scores; four independent chains of 3-input max
             float m_blk = -INFINITY;
@@ -316,26 +358,39 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
             if (i > 0 && __any_sync(0xffffffffu, m_new != m_run)) {
                 // O is complete once P.V of the previous block has retired
-                bool got = ptx::mbar_wait(p_free(pb ^ 1), (uint32_t)((i - 1) >> 1) & 1u, abort_flag);
-                if (!__all_sync(0xffffffffu, got)) return false;
+                ok = ptx::mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
                 ptx::tcgen05_fence_after_sync();
 #pragma unroll 1
-                for (int h = 0; h < kAttnD / 32; ++h) {
-                    uint32_t orow[32];
+                for (int h = 0; h < kAttnD / 16; ++h) {
+                    uint32_t orow[16];
                     __syncwarp();
-                    ptx::tmem_ld_32x32b_x32(t_lane + kAttnOCol + h * 32, orow);
+                    ptx::tmem_ld_32x32b_x16(t_lane + kAttnOCol + h * 16, orow);
                     ptx::tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) orow[j] = __float_as_uint(__uint_as_float(orow[j]) * alpha);
-                    ptx::tmem_st_32x32b_x32(t_lane + kAttnOCol + h * 32, orow);
+                    for (int j = 0; j < 16; ++j) orow[j] = __float_as_uint(__uint_as_float(orow[j]) * alpha);
+                    ptx::tmem_st_32x32b_x16(t_lane + kAttnOCol + h * 16, orow);
                 }
                 ptx::tmem_wait_st();
+                ptx::tcgen05_fence_before_sync();
             }
-            if (i >= 2) {
-                // P[pb] was the A operand of P.V of block i-2
-                bool got = ptx::mbar_wait(p_free(pb), (uint32_t)((i - 2) >> 1) & 1u, abort_flag);
-                if (!__all_sync(0xffffffffu, got)) return false;
-            }
+            // P[pb] was last read by P.V of block i-2.  That MMA was issued before Q.K^T of block
+            // i, whose completion (s_full, phase i) this warp observed during the previous step,
+            // and MMAs of one thread retire in order -- so the buffer is free without a wait.
+
+            // half h of `cur` is dead once its exps are done: refill it with block i+1
+            auto refill = [&](int h) -> bool {
+                if (!prefetch) return true;
+                if (h == 0) {
+                    bool got = ptx::mbar_wait(s_full, (uint32_t)(i + 1) & 1u, abort_flag);
+                    if (!__all_sync(0xffffffffu, got)) return false;
+                    ptx::tcgen05_fence_after_sync();
+                }
+                __syncwarp();
+                ptx::tmem_ld_32x32b_x32(t_lane + h * 32, cur[h]);
+                return true;
+            };
 
             // p = 2^(s*c - m*c), fp32 row sum, e4m3 P into the swizzled smem tile
             float row_sum = 0.f;
@@ -357,12 +412,12 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                                 pv[e] = fast_exp2(__fsub_rn(__fmul_rn(sv, c), m_scaled));
                                 row_sum += pv[e];
                             }
-                            w[q] = (uint32_t)float2_to_e4m3x2_sat(pv[0], pv[1]) |
-                                   ((uint32_t)float2_to_e4m3x2_sat(pv[2], pv[3]) << 16);
+                            w[q] = pack4_e4m3(pv[0], pv[1], pv[2], pv[3]);
                         }
                         const uint32_t chunk = (uint32_t)(h * 2 + g) ^ swz;
                         *reinterpret_cast<uint4*>(p_row + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
+                    if (!refill(h)) { ok = false; break; }
                 }
             } else {
                 const float2 c2 = make_float2(c, c);
@@ -382,40 +437,29 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                             const float2 p1 = make_float2(fast_exp2(e1.x), fast_exp2(e1.y));
                             sum_a = fadd2(sum_a, p0);
                             sum_b = fadd2(sum_b, p1);
-                            w[q] = (uint32_t)float2_to_e4m3x2_sat(p0.x, p0.y) |
-                                   ((uint32_t)float2_to_e4m3x2_sat(p1.x, p1.y) << 16);
+                            w[q] = pack4_e4m3(p0.x, p0.y, p1.x, p1.y);
                         }
                         const uint32_t chunk = (uint32_t)(h * 2 + g) ^ swz;
                         *reinterpret_cast<uint4*>(p_row + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
+                    if (!refill(h)) { ok = false; break; }
                 }
                 row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
             }
+            if (!ok) break;
             l_run = l_run * alpha + row_sum;
             m_run = m_new;
             ptx::fence_proxy_async_smem();                     // P visible to the tensor core's smem reads
-            ptx::tcgen05_fence_before_sync();                  // orders the O rescale before the signal
-            ptx::mbar_arrive(p_full(pb));
-            return true;
-        };
-
-        uint32_t s_a[2][32], s_b[2][32];
-        if (nblk > 0) {
-            ok = ptx::mbar_wait(s_full(0), 0, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                ptx::tcgen05_fence_after_sync();
-                ptx::tmem_ld_32x32b_x32(t_lane, s_a[0]);
-                ptx::tmem_ld_32x32b_x32(t_lane + 32, s_a[1]);
+            warp_arrive(p_full(pb), lane);
+            if (prefetch) {
+                ptx::tmem_wait_ld();                           // block i+1 is in registers
+                ptx::tcgen05_fence_before_sync();
+                warp_arrive(s_free, lane);                     // Q.K^T of block i+2 may overwrite S
             }
-        }
-        for (int i = 0; ok && i < nblk; i += 2) {
-            ok = step(i, s_a, s_b);
-            if (ok && i + 1 < nblk) ok = step(i + 1, s_b, s_a);
         }
 
         // epilogue: O / l
-        if (ok && nblk > 0) ok = ptx::mbar_wait(p_free((nblk - 1) & 1), (uint32_t)((nblk - 1) >> 1) & 1u, abort_flag);
+        if (ok && nblk > 0) ok = ptx::mbar_wait(pv_done, (uint32_t)(nblk - 1) & 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             ptx::tcgen05_fence_after_sync();
@@ -433,9 +477,6 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     for (int j = 0; j < 32; ++j) orow[j] = 0u;
                 }
                 if (row < p.M) {
-                    float y[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(orow[j]) * inv;
                     if (p.out_e4m3) {
                         uint8_t* o = reinterpret_cast<uint8_t*>(p.out) + out_off + h * 32;
 #pragma unroll
@@ -444,8 +485,8 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 const int j = v4 * 16 + q * 4;
-                                w[q] = (uint32_t)float2_to_e4m3x2_sat(y[j], y[j + 1]) |
-                                       ((uint32_t)float2_to_e4m3x2_sat(y[j + 2], y[j + 3]) << 16);
+                                w[q] = pack4_e4m3(__uint_as_float(orow[j]) * inv, __uint_as_float(orow[j + 1]) * inv,
+                                                  __uint_as_float(orow[j + 2]) * inv, __uint_as_float(orow[j + 3]) * inv);
                             }
                             reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
@@ -457,7 +498,8 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 const int j = v4 * 8 + q * 2;
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(y[j], y[j + 1]);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(orow[j]) * inv,
+                                                                          __uint_as_float(orow[j + 1]) * inv);
                                 w[q] = *reinterpret_cast<uint32_t*>(&b2);
                             }
                             reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -465,18 +507,10 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     }
                 }
             }
-        } else if (p.status != nullptr && threadIdx.x == 64) {
+        } else if (p.status != nullptr && threadIdx.x == 128) {
             atomicExch(p.status, Q8K_STATUS_TIMEOUT | (6 << 8));
         }
-    }
-
-    // ---------------------------------------------------- teardown
-    ptx::tcgen05_fence_before_sync();
-    __syncthreads();
-    if (warp == 1) {
-        __syncwarp();
-        ptx::tcgen05_fence_after_sync();
-        ptx::tmem_dealloc<kAttnTmemCols>(tmem_base);
+        teardown_barrier();
     }
 }
 
@@ -610,6 +644,14 @@ extern "C" int q8k_flash_attention(const void* q, const void* k, const void* vt,
     p.scale_log2 = (float)((double)softmax_scale * 1.4426950408889634);
     p.out_e4m3 = out_dtype == Q8K_DT_E4M3;
 
+    // The warpgroups re-budget registers with setmaxnreg; an increase blocks until the CTA's pool
+    // has room, so the pool the kernel was compiled for must cover the three budgets.
+    static_assert(2 * kAttnRegsLaunch == kAttnRegsIo + kAttnRegsSoftmax, "register budgets");
+    cudaFuncAttributes fattr;
+    Q8K_CUDA_OK(cudaFuncGetAttributes(&fattr, flash_attn_fp8_kernel));
+    Q8K_REQUIRE(fattr.numRegs >= kAttnRegsLaunch, Q8K_ERR_CUDA,
+                "%s: kernel was built with %d registers per thread, %d needed for the warpgroup budgets", op,
+                fattr.numRegs, kAttnRegsLaunch);
     Q8K_CUDA_OK(cudaFuncSetAttribute(flash_attn_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::kDynamic));
     dim3 grid((unsigned)((M + kAttnBM - 1) / kAttnBM), (unsigned)BH);
     flash_attn_fp8_kernel<<<grid, kAttnThreads, AttnSmem::kDynamic, (cudaStream_t)stream>>>(tq, tk, tv, p);

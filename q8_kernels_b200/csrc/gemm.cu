@@ -105,7 +105,7 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(tmem_full_bar(a), 1);
-            ptx::mbar_init(tmem_empty_bar(a), kGemmEpilogueThreads);
+            ptx::mbar_init(tmem_empty_bar(a), kGemmEpilogueThreads / 32);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -284,7 +284,8 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 __syncwarp();                                  // reconverge before the next warp-collective TMEM op
             }
             ptx::tcgen05_fence_before_sync();
-            ptx::mbar_arrive(tmem_empty_bar(acc));
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tmem_empty_bar(acc));
         }
         if (!ok && p.status != nullptr && epi_tid == 0) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (3 << 8));
     }

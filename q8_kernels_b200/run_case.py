@@ -26,6 +26,7 @@ def main() -> None:
     ap.add_argument("--b", type=int, default=1)
     ap.add_argument("--h", type=int, default=8)
     ap.add_argument("--s", type=int, default=4096)
+    ap.add_argument("--skv", type=int, default=0, help="key/value length (default: --s, or 128 for cross_attention)")
     ap.add_argument("--rows", type=int, default=24576)
     ap.add_argument("--dim", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=3)
@@ -51,7 +52,7 @@ def main() -> None:
              (lambda: mm(xq, wq, xs, ws, False, torch.bfloat16))
         work = 2.0 * a.m * a.k * a.n / 1e12
     elif a.case in ("attention", "cross_attention"):
-        skv = a.s if a.case == "attention" else 128
+        skv = a.skv if a.skv > 0 else (a.s if a.case == "attention" else 128)
         q = torch.randn(a.b, a.s, a.h * 64, generator=g, device=dev).to(torch.bfloat16).view(a.b, a.s, a.h, 64).transpose(1, 2)
         k = torch.randn(a.b, skv, a.h * 64, generator=g, device=dev).to(torch.bfloat16).view(a.b, skv, a.h, 64).transpose(1, 2)
         v = torch.randn(a.b, skv, a.h * 64, generator=g, device=dev).to(torch.bfloat16).view(a.b, skv, a.h, 64).transpose(1, 2)
