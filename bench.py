@@ -357,6 +357,27 @@ def bench_detail(q8, dev, peaks, steps):
         del xs, cos
         torch.cuda.empty_cache()
     out["rowwise"] = rw
+
+    # one video through the 28-block DiT stack (config 5): INT8 linears, FP8 Hadamard attention
+    cfg = q8.blocks.LTXStackConfig()
+    stack = q8.blocks.random_init_(q8.blocks.LTXStack(cfg), seed=11, device=dev)
+    S, T = 6144, 128
+    x = torch.randn(1, S, cfg.inner_dim, generator=g, device=dev).to(torch.bfloat16)
+    text = torch.randn(1, T, cfg.caption_channels, generator=g, device=dev).to(torch.bfloat16)
+    ts = (torch.randn(1, 1, 6 * cfg.inner_dim, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    grid = q8.blocks.latent_grid(16, 16, 24, device=dev)
+    lens = torch.tensor([97], dtype=torch.int32, device=dev)
+    with torch.no_grad():
+        ms_stack = timed(lambda: stack(x, grid, text, lens, ts, attn_type="q8_kernels"), 3)
+        freqs = stack.freqs_cis(grid)
+        tproj = stack.caption_projection(text)
+        blk = stack.transformer_blocks[0]
+        ms_blk = timed(lambda: blk(x, freqs, None, tproj, lens, ts, attn_type="q8_kernels"), 10)
+    flop_blk = 2.0 * S * (6 * 2048 ** 2 + 2 * 2048 * 8192) + 2.0 * T * 2 * 2048 ** 2 + 4.0 * 32 * S * S * 64 \
+        + 4.0 * 32 * S * T * 64
+    out["dit"] = {"block_ms": round(ms_blk, 4), "stack28_ms": round(ms_stack, 3),
+                  "block_tflops": round(flop_blk / ms_blk / 1e9, 1), "tokens": S, "text_tokens": T,
+                  "linears": "int8", "attention": "fp8 hadamard"}
     return out
 
 

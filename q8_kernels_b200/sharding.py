@@ -1,0 +1,78 @@
+"""Multi-GPU sharding of the DiT path: one process per GPU, ``torch.distributed``
+(NCCL over NVLink on GPUs, gloo on CPU for tests).
+
+Two ways the path shards, neither with a collective inside the hot loops:
+
+* by video: each rank runs the whole stack on its own videos; one
+  ``all_gather_into_tensor`` of the final latents at the end;
+* by attention head: linears, q/k RMSNorm (it spans all heads) and RoPE run
+  replicated, each rank computes attention for H/world heads and the per-rank
+  channel slices are all-gathered before ``to_out`` (one collective per
+  self-attention).
+
+The reference has no multi-GPU code; this module is new host-side logic.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def video_shard(num_videos: int, rank: int, world: int) -> range:
+    """Contiguous block of video indices owned by ``rank`` (sizes differ by at most one)."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    base, extra = divmod(num_videos, world)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def head_shard(num_heads: int, rank: int, world: int) -> Tuple[int, int]:
+    """(rank, world) pair accepted by ``Attention.forward(head_shard=...)`` after checking divisibility."""
+    if num_heads % world != 0:
+        raise ValueError(f"{num_heads} heads do not divide over {world} ranks")
+    if not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} for world {world}")
+    return rank, world
+
+
+def head_slice(num_heads: int, rank: int, world: int) -> slice:
+    head_shard(num_heads, rank, world)
+    per = num_heads // world
+    return slice(rank * per, (rank + 1) * per)
+
+
+def gather_heads(x_local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """[B, S, C/world] per rank -> [B, S, C] on every rank, channel blocks in rank order."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return x_local
+    x_local = x_local.contiguous()
+    B, S, c = x_local.shape
+    buf = torch.empty((world * B, S, c), dtype=x_local.dtype, device=x_local.device)   # rank blocks along dim 0
+    if x_local.dtype == torch.float8_e4m3fn:                    # collectives move bytes
+        dist.all_gather_into_tensor(buf.view(torch.uint8), x_local.view(torch.uint8), group=group)
+    else:
+        dist.all_gather_into_tensor(buf, x_local, group=group)
+    # [world, B, S, c] -> [B, S, world, c] -> [B, S, C]
+    return buf.view(world, B, S, c).permute(1, 2, 0, 3).reshape(B, S, world * c)
+
+
+def gather_videos(x_local: torch.Tensor, counts: List[int], group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Final gather of the by-video sharding: per-rank [n_r, ...] -> [sum n_r, ...] on every rank."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return x_local
+    if len(set(counts)) == 1:
+        out = torch.empty((sum(counts),) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=x_local.device)
+        dist.all_gather_into_tensor(out, x_local.contiguous(), group=group)
+        return out
+    # uneven split: pad every rank to the largest share, gather once, drop the padding
+    most = max(counts)
+    padded = torch.zeros((most,) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=x_local.device)
+    padded[: x_local.shape[0]] = x_local
+    out = torch.empty((world * most,) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=x_local.device)
+    dist.all_gather_into_tensor(out, padded, group=group)
+    return torch.cat([out[r * most: r * most + n] for r, n in enumerate(counts)], dim=0)

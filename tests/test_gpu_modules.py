@@ -121,3 +121,43 @@ def test_ltx_block_against_oracle(q8, cuda_device, attn_type):
     # errors compound through 10 linears, two attentions and bf16 elementwise ops: bf16-level agreement
     err = Hp.rel_fro(got.float(), ref.float())
     assert err < 1.5e-2, f"rel fro {err:.3e}"
+
+
+def test_freqs_cis_matches_reference_table(q8, cuda_device):
+    """Product RoPE table vs the vectors produced by the reference's own precompute_freqs_cis."""
+    import golden_io as G
+    d = G.load("ref_freqs_cis.npz")
+    grid = G.t(d["grid"]).to(cuda_device)
+    cos, sin = q8.blocks.precompute_freqs_cis(grid, 2048)
+    # GPU cos/sin differ from the CPU libm by an ulp or two in fp32
+    assert torch.allclose(cos.cpu(), G.t(d["cos"]), atol=2e-6, rtol=0)
+    assert torch.allclose(sin.cpu(), G.t(d["sin"]), atol=2e-6, rtol=0)
+    g2 = q8.blocks.latent_grid(2, 3, 4, device=cuda_device)
+    assert torch.equal(g2.cpu(), G.t(d["grid"]))
+
+
+def test_ltx_stack_small_against_oracle(q8, cuda_device):
+    cfg = q8.blocks.LTXStackConfig(num_layers=2, num_attention_heads=4, attention_head_dim=64,
+                                   cross_attention_dim=256, caption_channels=128)
+    stack = q8.blocks.random_init_(q8.blocks.LTXStack(cfg), seed=5, device=cuda_device)
+    g = Hp.gen(31)
+    S, T = 4 * 4 * 6, 40
+    x = torch.randn(1, S, 256, generator=g).to(torch.bfloat16)
+    text = torch.randn(1, T, 128, generator=g).to(torch.bfloat16)
+    timestep = (torch.randn(1, 1, 6 * 256, generator=g) * 0.1).to(torch.bfloat16)
+    grid = q8.blocks.latent_grid(4, 4, 6)
+    lens = torch.tensor([29], dtype=torch.int32)
+    d = cuda_device
+    got = stack(x.to(d), grid.to(d), text.to(d), lens.to(d), timestep.to(d), attn_type="q8_kernels")
+    # oracle: same weights, CPU
+    sd = {k: v.detach().cpu() for k, v in stack.state_dict().items()}
+    cos, sin = O.precompute_freqs_cis(grid, dim=256)
+    proj = torch.nn.functional.linear(text.float(), sd["caption_projection.weight"].float(),
+                                      sd["caption_projection.bias"].float()).to(torch.bfloat16)
+    h = x
+    for i in range(2):
+        pre = f"transformer_blocks.{i}."
+        bsd = {k[len(pre):]: v for k, v in sd.items() if k.startswith(pre)}
+        h = OB.ltx_block(bsd, h, (cos, sin), None, proj, lens, timestep, num_heads=4, head_dim=64)
+    err = Hp.rel_fro(got.float(), h.float())
+    assert got.shape == (1, S, 256) and err < 2e-2, f"rel fro {err:.3e}"
