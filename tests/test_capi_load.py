@@ -91,3 +91,15 @@ def test_python_api_surface_matches_reference():
               "attn2.to_k.bias", "attn1.to_out.weight", "ff.act.proj.weight", "ff.proj_down.scales"):
         assert k in keys, k
     assert "norm1.weight" not in keys                                      # norm_affine=False
+
+
+def test_rope_table_on_cpu_matches_reference_vectors():
+    """The product's RoPE table is pure torch: on the CPU it must reproduce, bit for bit, the table
+    the reference's own precompute_freqs_cis produced for the golden fixture."""
+    import golden_io as G
+    import q8_kernels_b200 as q8
+    d = G.load("ref_freqs_cis.npz")
+    cos, sin = q8.blocks.precompute_freqs_cis(G.t(d["grid"]), 2048)
+    Hp.assert_bit_equal(cos, G.t(d["cos"]), "cos")
+    Hp.assert_bit_equal(sin, G.t(d["sin"]), "sin")
+    assert torch.equal(q8.blocks.latent_grid(2, 3, 4), G.t(d["grid"]))

@@ -129,9 +129,10 @@ def test_freqs_cis_matches_reference_table(q8, cuda_device):
     d = G.load("ref_freqs_cis.npz")
     grid = G.t(d["grid"]).to(cuda_device)
     cos, sin = q8.blocks.precompute_freqs_cis(grid, 2048)
-    # GPU cos/sin differ from the CPU libm by an ulp or two in fp32
-    assert torch.allclose(cos.cpu(), G.t(d["cos"]), atol=2e-6, rtol=0)
-    assert torch.allclose(sin.cpu(), G.t(d["sin"]), atol=2e-6, rtol=0)
+    # the highest frequencies reach phases of ~1.5e4 rad, where one fp32 ulp of the frequency
+    # (GPU vs CPU pow) moves the phase by ~1e-3 rad; the CPU path is checked bit for bit elsewhere
+    assert torch.allclose(cos.cpu(), G.t(d["cos"]), atol=5e-3, rtol=0)
+    assert torch.allclose(sin.cpu(), G.t(d["sin"]), atol=5e-3, rtol=0)
     g2 = q8.blocks.latent_grid(2, 3, 4, device=cuda_device)
     assert torch.equal(g2.cpu(), G.t(d["grid"]))
 
