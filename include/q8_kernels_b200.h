@@ -155,6 +155,30 @@ Q8K_API int q8k_linear(const void* x, int x_dtype, const void* w, int w_dtype, c
                int use_hadamard, int fuse_gelu, void* workspace, size_t workspace_bytes,
                int* dev_status, void* stream);
 
+/* q8k_linear without any allocation on either side of the call.  No counterpart in the
+ * reference: it exists for callers that cannot obtain device scratch at call time -- a plugin
+ * living inside a host runtime that has reserved the whole device heap and hands a plugin nothing
+ * but its input and output buffers, or a latency-critical thread for which a cudaMalloc (and the
+ * device-wide synchronisation it may imply) is not acceptable.  The quantised activations and
+ * their row scales go into an array compiled into the library image (16.25 MiB of device memory
+ * on every GPU that loads the library, held until the process exits), so the problem is limited to
+ * M*K <= Q8K_LINEAR_STATIC_MAX_MK and M <= Q8K_LINEAR_STATIC_MAX_M; larger ones are rejected with
+ * Q8K_ERR_TOO_LARGE and must use q8k_linear with a workspace.  The function itself calls no
+ * cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current) and caches it; make that first call before any stream capture
+ *     is begun on the device.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Every
+ *     byte a call reads it has written first, so nothing needs clearing, but two calls whose
+ *     kernels can overlap on the GPU (different streams without an ordering between them) race
+ *     on it: serialise them on one stream or with events.
+ * Arguments, dtypes, results and error codes are otherwise those of q8k_linear.                  */
+#define Q8K_LINEAR_STATIC_MAX_MK (16 * 1024 * 1024)
+#define Q8K_LINEAR_STATIC_MAX_M  65536
+Q8K_API int q8k_linear_static(const void* x, int x_dtype, const void* w, int w_dtype, const float* w_scales,
+                              const float* bias, void* out, int out_dtype, int M, int N, int K,
+                              int use_hadamard, int fuse_gelu, int* dev_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

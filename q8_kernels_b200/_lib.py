@@ -50,6 +50,8 @@ SIGNATURES = {
     "q8k_linear_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "q8k_linear": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_ptr, _c_size, _c_ptr, _c_ptr]),
+    "q8k_linear_static": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                   _c_int, _c_int, _c_int, _c_ptr, _c_ptr]),
 }
 
 
