@@ -130,6 +130,16 @@ Q8K_API int q8k_flash_attention(const void* q, const void* k, const void* vt, vo
                         int B, int H, int M, int N, float softmax_scale, const int* key_lens,
                         int* dev_status, void* stream);
 
+/* Same kernel with an explicit output layout: element (b, h, row, d) is written at
+ * out[b*out_stride_b + h*out_stride_h + row*out_stride_s + d] (strides in elements, multiples of 16).
+ * With strides (M*H*64, 64, H*64) the result lands as [B, M, H*64], which is what the attention
+ * module feeds to its output projection, so the transpose copy of
+ * q8_kernels/modules/attention.py:101-103 disappears.                                            */
+Q8K_API int q8k_flash_attention_strided(const void* q, const void* k, const void* vt, void* out, int out_dtype,
+                                int B, int H, int M, int N, int64_t out_stride_b, int64_t out_stride_h,
+                                int64_t out_stride_s, float softmax_scale, const int* key_lens,
+                                int* dev_status, void* stream);
+
 /* Pre-pass of the attention call: from bf16 q,k,v given as strided [B,S,H,64]
  * views (strides in elements, last dim contiguous) produce q8,k8 [B,H,S,64]
  * e4m3 (Hadamard-rotated times qk_scale when apply_hadamard, else plain cast)

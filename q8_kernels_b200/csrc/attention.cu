@@ -73,6 +73,7 @@ struct AttnParams {
     int B, H, M, N;
     float scale_log2;                      // softmax_scale * log2(e)
     int out_e4m3;
+    int64_t out_stride_b, out_stride_h, out_stride_s;   // output strides in elements (head dim contiguous)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -464,7 +465,8 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (ok) {
             ptx::tcgen05_fence_after_sync();
             const float inv = (l_run == 0.f || l_run != l_run) ? 1.f : 1.f / l_run;
-            const int64_t out_off = ((int64_t)bh * p.M + row) * kAttnD;
+            const int64_t out_off = (int64_t)b * p.out_stride_b + (int64_t)(bh - b * p.H) * p.out_stride_h +
+                                    (int64_t)row * p.out_stride_s;
 #pragma unroll 1
             for (int h = 0; h < kAttnD / 32; ++h) {
                 uint32_t orow[32];
@@ -604,6 +606,14 @@ using namespace q8k;
 extern "C" int q8k_flash_attention(const void* q, const void* k, const void* vt, void* out, int out_dtype,
                                    int B, int H, int M, int N, float softmax_scale, const int* key_lens,
                                    int* dev_status, void* stream) {
+    return q8k_flash_attention_strided(q, k, vt, out, out_dtype, B, H, M, N, (int64_t)H * M * 64, (int64_t)M * 64, 64,
+                                       softmax_scale, key_lens, dev_status, stream);
+}
+
+extern "C" int q8k_flash_attention_strided(const void* q, const void* k, const void* vt, void* out, int out_dtype,
+                                           int B, int H, int M, int N, int64_t out_stride_b, int64_t out_stride_h,
+                                           int64_t out_stride_s, float softmax_scale, const int* key_lens,
+                                           int* dev_status, void* stream) {
     const char* op = "flash_attention";
     Q8K_REQUIRE(q && k && vt && out, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
     Q8K_REQUIRE(B > 0 && H > 0 && M >= 0 && N > 0, Q8K_ERR_INVALID_ARG, "%s: bad shape B=%d H=%d M=%d N=%d", op, B, H, M, N);
@@ -612,6 +622,8 @@ extern "C" int q8k_flash_attention(const void* q, const void* k, const void* vt,
     Q8K_REQUIRE(out_dtype == Q8K_DT_E4M3 || out_dtype == Q8K_DT_BF16, Q8K_ERR_UNSUPPORTED,
                 "%s: output dtype %d is not e4m3 or bf16", op, out_dtype);
     Q8K_REQUIRE((int64_t)B * H <= 65535, Q8K_ERR_TOO_LARGE, "%s: B*H = %lld exceeds 65535", op, (long long)B * H);
+    Q8K_REQUIRE(out_stride_b % 16 == 0 && out_stride_h % 16 == 0 && out_stride_s % 16 == 0 && out_stride_s >= 64,
+                Q8K_ERR_INVALID_ARG, "%s: output strides must be multiples of 16 elements", op);
     if (M == 0) return Q8K_OK;
     const int n_pad = (N + 15) / 16 * 16;
     const uint64_t BH = (uint64_t)B * H;
@@ -643,6 +655,7 @@ extern "C" int q8k_flash_attention(const void* q, const void* k, const void* vt,
     p.B = B; p.H = H; p.M = M; p.N = N;
     p.scale_log2 = (float)((double)softmax_scale * 1.4426950408889634);
     p.out_e4m3 = out_dtype == Q8K_DT_E4M3;
+    p.out_stride_b = out_stride_b; p.out_stride_h = out_stride_h; p.out_stride_s = out_stride_s;
 
     // The warpgroups re-budget registers with setmaxnreg; an increase blocks until the CTA's pool
     // has room, so the pool the kernel was compiled for must cover the three budgets.

@@ -11,11 +11,11 @@
 //  * rows of <= 256 elements: a group of G = n/8 lanes owns a row (8 elements
 //    per lane, one 16-byte load), 32/G rows per warp; stages 0-2 in registers,
 //    the rest by xor-shuffles inside the group.
-//  * rows of 512 .. 16384 elements: warp `a` of the CTA owns elements
-//    [512a, 512a+512), 16 consecutive elements per lane; stages 0-3 in
-//    registers, 4-8 by xor-shuffles, then one swizzled shared-memory exchange
-//    after which each thread holds all `A` values of a few columns and finishes
-//    stages 9+ in registers, storing straight from that layout.
+//  * rows of 512 .. 16384 elements: 16-64 threads per row with 32-128 values
+//    each; the first 5-7 stages run in registers on consecutive elements, the
+//    rest after one swizzled shared-memory exchange (two for 16384), all on
+//    packed fp32 pairs; no shuffles.  Shared-memory traffic, not issue slots or
+//    HBM, is what this schedule is sized for: 12 bytes per element in total.
 
 #include <type_traits>
 #include "common.cuh"
@@ -130,147 +130,290 @@ hadamard_small_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* 
 }
 
 // ------------------------------------------------------------------ large rows
-__device__ __forceinline__ int swizzle_chunk(int q) {          // q = float4 index inside a 512-float warp-row
-    return (q & ~3) | ((q & 3) ^ ((q >> 3) & 3));
+// One CTA per row of N = 2^LOG_N (padded) elements, T = N / V threads, V = 2^LOG_V values per
+// thread.  The row is staged raw in shared memory by coalesced loads; each thread then owns V
+// consecutive elements and runs stages 0 .. LOG_V-1 in registers.  The remaining stages run in
+// phases of up to LOG_V-2 bits: the row is exchanged through shared memory (fp32, natural element
+// order, float4 chunks XOR-swizzled so that both sides are conflict free) into a layout where a
+// thread owns 2^b groups x C consecutive elements, the groups being the butterfly partners.
+// Butterflies work on packed fp32 pairs (add/sub.f32x2), so a stage costs half an instruction per
+// element; only the stride-1 stage is scalar.
+
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fsub2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("sub.rn.f32x2 %0, %1, %2;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
 }
 
-template <typename Tin, typename Tout, int LOG_A, Epilogue EPI>
-__global__ void __launch_bounds__(32 << LOG_A)
-hadamard_large_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __restrict__ scales,
-                      int dim, int64_t x_row_stride, float scale) {
-    constexpr int A = 1 << LOG_A;                  // warps per CTA == 512-element segments per row
-    constexpr int T = 32 * A;
-    constexpr int NB = (A <= 16) ? 16 / A : 1;     // columns per thread after the exchange
-    constexpr int ACTIVE = 512 / NB;               // threads that own columns after the exchange
-    extern __shared__ __align__(16) float xch[];   // [A][512], float4 chunks swizzled
-    __shared__ float red[32];
+__device__ __forceinline__ int swz4(int q) { return q ^ ((q >> 3) & 7); }      // float4-chunk swizzle
 
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int64_t row = blockIdx.x;
-    const Tin* xr = x + row * x_row_stride;
-    const int e0 = warp * 512 + lane * 16;
+// Layout of a phase that butterflies bits [LO, LO+B): thread t owns groups j = 0 .. 2^B-1 of
+// C = V >> B consecutive elements each.  The thread index supplies the other bits of the
+// element index: its low LO-log2(C) bits sit below the group bits, the rest above them.
+template <int LOG_V, int B, int LO>
+struct PhaseLayout {
+    static constexpr int LOG_C = LOG_V - B;
+    static constexpr int C = 1 << LOG_C;
+    static constexpr int G = 1 << B;
+    static constexpr int BITS = B;
+    static_assert(LO >= LOG_C, "group bits must lie above the run bits");
+    __device__ static __forceinline__ int elem(int t, int j) {
+        constexpr int LOWT = LO - LOG_C;
+        return ((t & ((1 << LOWT) - 1)) << LOG_C) + (j << LO) + ((t >> LOWT) << (LO + B));
+    }
+};
 
-    float v[16];
+// registers (layout L) -> shared memory, natural element order (runs of 2 use float2 accesses
+// inside the swizzled float4 chunk)
+template <typename L, int V>
+__device__ __forceinline__ void exchange_write(float* xch, const float (&v)[V], int t) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = 0.f;
-    {
-        float h[8];
-        if (e0 < dim) {
-            load_vec<Tin, 8>(xr + e0, h);
+    for (int j = 0; j < L::G; ++j) {
+        const int e = L::elem(t, j);
+        if constexpr (L::C >= 4) {
+            float4* x4 = reinterpret_cast<float4*>(xch);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = h[j];
-        }
-        if (e0 + 8 < dim) {
-            load_vec<Tin, 8>(xr + e0 + 8, h);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[8 + j] = h[j];
+            for (int k = 0; k < L::C / 4; ++k)
+                x4[swz4((e >> 2) + k)] = make_float4(v[j * L::C + 4 * k], v[j * L::C + 4 * k + 1],
+                                                     v[j * L::C + 4 * k + 2], v[j * L::C + 4 * k + 3]);
+        } else {
+            float2* x2 = reinterpret_cast<float2*>(xch);
+            x2[swz4(e >> 2) * 2 + ((e >> 1) & 1)] = make_float2(v[j * 2], v[j * 2 + 1]);
         }
     }
-
-    fwht_regs<16>(v);
+}
+template <typename L, int V>
+__device__ __forceinline__ void exchange_read(const float* xch, float (&v)[V], int t) {
 #pragma unroll
-    for (int m = 1; m < 32; m <<= 1) fwht_lanes<16>(v, lane, m);
-
-    if constexpr (A == 1) {
-        // the whole row lives in one warp: finish from the load layout
-        float amax = 0.f;
+    for (int j = 0; j < L::G; ++j) {
+        const int e = L::elem(t, j);
+        if constexpr (L::C >= 4) {
+            const float4* x4 = reinterpret_cast<const float4*>(xch);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            v[j] = __fmul_rn(v[j], scale);
-            if constexpr (EPI == Epilogue::Quant) {
-                v[j] = round_through<Tin>(v[j]);
-                if (e0 + j < dim) amax = fmaxf(amax, fabsf(v[j]));
+            for (int k = 0; k < L::C / 4; ++k) {
+                const float4 f = x4[swz4((e >> 2) + k)];
+                v[j * L::C + 4 * k] = f.x; v[j * L::C + 4 * k + 1] = f.y;
+                v[j * L::C + 4 * k + 2] = f.z; v[j * L::C + 4 * k + 3] = f.w;
             }
-        }
-        float lo[8], hi[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { lo[j] = v[j]; hi[j] = v[8 + j]; }
-        if constexpr (EPI == Epilogue::Cast) {
-            Tout* o = out + row * (int64_t)dim + e0;
-            if (e0 < dim) store_elems<Tout, 8>(o, lo);
-            if (e0 + 8 < dim) store_elems<Tout, 8>(o + 8, hi);
         } else {
-            amax = warp_max(amax);
-            const float qmax = std::is_same_v<Tout, int8_t> ? 127.0f : 448.0f;
-            const float qscale = __fdiv_rn(qmax, amax);
-            Tout* o = out + row * (int64_t)dim + e0;
-            if (e0 < dim) store_quant<Tout, 8>(o, lo, qscale, amax == 0.f);
-            if (e0 + 8 < dim) store_quant<Tout, 8>(o + 8, hi, qscale, amax == 0.f);
-            if (lane == 0) scales[row] = __fdiv_rn(1.0f, qscale);
+            const float2* x2 = reinterpret_cast<const float2*>(xch);
+            const float2 f = x2[swz4(e >> 2) * 2 + ((e >> 1) & 1)];
+            v[j * 2] = f.x; v[j * 2 + 1] = f.y;
         }
-        return;
-    } else {
-        // exchange: thread (warp, lane) publishes its 16 values, then thread `tid`
-        // collects columns [tid*NB, tid*NB+NB) of every segment.
-        float4* xch4 = reinterpret_cast<float4*>(xch);
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-            xch4[warp * 128 + swizzle_chunk(lane * 4 + c)] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-        __syncthreads();
+    }
+}
 
-        const int tid = threadIdx.x;
-        const bool active = tid < ACTIVE;
-        const int b0 = tid * NB;                    // first column owned
-        float w[NB][A];                             // w[i][a] = value of column b0+i in segment a
-        if (active) {
+// butterflies between groups (stride = whole groups of C >= 4 elements): all packed
+template <typename L, int V>
+__device__ __forceinline__ void butterfly_groups(float (&v)[V]) {
 #pragma unroll
-            for (int a = 0; a < A; ++a) {
-                if constexpr (NB >= 4) {
+    for (int s = 0; s < L::BITS; ++s) {
+        const int gs = 1 << s;
 #pragma unroll
-                    for (int c = 0; c < NB / 4; ++c) {
-                        const float4 f = xch4[a * 128 + swizzle_chunk(b0 / 4 + c)];
-                        w[4 * c][a] = f.x; w[4 * c + 1][a] = f.y; w[4 * c + 2][a] = f.z; w[4 * c + 3][a] = f.w;
-                    }
-                } else {
+        for (int h = 0; h < L::G / 2; ++h) {
+            const int lo = h & (gs - 1);
+            const int j = ((h - lo) << 1) + lo;
 #pragma unroll
-                    for (int i = 0; i < NB; ++i) {
-                        const int b = b0 + i;
-                        w[i][a] = xch[a * 512 + swizzle_chunk(b >> 2) * 4 + (b & 3)];
-                    }
+            for (int c = 0; c < L::C; c += 2) {
+                const float2 a = make_float2(v[j * L::C + c], v[j * L::C + c + 1]);
+                const float2 b = make_float2(v[(j + gs) * L::C + c], v[(j + gs) * L::C + c + 1]);
+                const float2 su = fadd2(a, b), di = fsub2(a, b);
+                v[j * L::C + c] = su.x; v[j * L::C + c + 1] = su.y;
+                v[(j + gs) * L::C + c] = di.x; v[(j + gs) * L::C + c + 1] = di.y;
+            }
+        }
+    }
+}
+
+// stages 0 .. log2(V)-1 over V consecutive elements: stride 1 scalar, the rest packed
+template <int V>
+__device__ __forceinline__ void butterfly_consecutive(float (&v)[V]) {
+#pragma unroll
+    for (int i = 0; i < V; i += 2) {
+        const float a = v[i], b = v[i + 1];
+        v[i] = __fadd_rn(a, b);
+        v[i + 1] = __fsub_rn(a, b);
+    }
+#pragma unroll
+    for (int st = 2; st < V; st <<= 1) {
+#pragma unroll
+        for (int h = 0; h < V / 2; h += 2) {                   // h, h+1 index two adjacent butterflies
+            const int lo = h & (st - 1);
+            const int i = ((h - lo) << 1) + lo;
+            const float2 a = make_float2(v[i], v[i + 1]);
+            const float2 b = make_float2(v[i + st], v[i + st + 1]);
+            const float2 su = fadd2(a, b), di = fsub2(a, b);
+            v[i] = su.x; v[i + 1] = su.y;
+            v[i + st] = di.x; v[i + st + 1] = di.y;
+        }
+    }
+}
+
+// Exact round-half-away-from-zero (C round()) of |y| < 2^22 with one add: adding the largest
+// float below 0.5 with y's sign and truncating gives floor(|y| + 0.5) for every fp32 y, ties
+// included (the sum of a tie k + 0.5 rounds up to k + 1, and 0.5 - 2^-25 stays below 1).
+__device__ __forceinline__ int round_half_away_int(float y) {
+    return __float2int_rz(__fadd_rn(y, copysignf(0.49999997f, y)));
+}
+
+template <typename Tq>
+__device__ __forceinline__ uint8_t quantize_fast(float y) {
+    if constexpr (std::is_same_v<Tq, int8_t>) return (uint8_t)(int8_t)round_half_away_int(y);
+    else return float_to_e4m3_c10(y);
+}
+
+template <typename Tin, typename Tout, int LOG_N, int LOG_V, int ROWS, Epilogue EPI>
+__global__ void __launch_bounds__(ROWS << (LOG_N - LOG_V))
+hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __restrict__ scales,
+                    int64_t rows, int dim, int64_t x_row_stride, float scale) {
+    constexpr int N = 1 << LOG_N;
+    constexpr int V = 1 << LOG_V;
+    constexpr int T = N / V;                                   // threads per row
+    constexpr int ITEMS = V / 8;                               // 8-element input items per thread
+    constexpr int R = LOG_N - LOG_V;                           // bits left after the register phase
+    constexpr int BMAX = LOG_V - 1;                            // keeps runs of >= 2 consecutive elements
+    constexpr int B1 = R < BMAX ? R : BMAX;
+    constexpr int B2 = R - B1;
+    static_assert(B2 <= BMAX, "row too long for this values-per-thread choice");
+    using L0 = PhaseLayout<LOG_V, 0, LOG_V>;                   // V consecutive elements
+    using L1 = PhaseLayout<LOG_V, B1, LOG_V>;
+    using L2 = PhaseLayout<LOG_V, B2, LOG_V + B1>;
+
+    extern __shared__ __align__(16) float xch_all[];           // ROWS x N floats
+    __shared__ float red[32];
+    const int t = threadIdx.x % T;
+    const int r_in_cta = threadIdx.x / T;
+    const int64_t row = (int64_t)blockIdx.x * ROWS + r_in_cta;
+    const bool row_ok = row < rows;
+    float* xch = xch_all + r_in_cta * N;
+    const Tin* xr = x + row * x_row_stride;
+
+    // coalesced load of raw 8-element items into shared memory, then V consecutive elements per thread
+    {
+        using Item = typename Vec<8 * sizeof(Tin)>::type;
+        Item* stage = reinterpret_cast<Item*>(xch);
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+            const int item = t + k * T;
+            Item val;
+            if (row_ok && item * 8 < dim) val = *reinterpret_cast<const Item*>(xr + item * 8);
+            else memset(&val, 0, sizeof(val));
+            stage[item ^ ((item / ITEMS) & (ITEMS - 1))] = val;   // spread a thread's ITEMS reads over the banks
+        }
+    }
+    __syncthreads();
+    float v[V];
+    {
+        using Item = typename Vec<8 * sizeof(Tin)>::type;
+        const Item* stage = reinterpret_cast<const Item*>(xch);
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+            const int item = t * ITEMS + k;
+            union { Item raw; Tin e[8]; } u;
+            u.raw = stage[item ^ (t & (ITEMS - 1))];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[k * 8 + j] = to_float<Tin>(u.e[j]);
+        }
+    }
+    butterfly_consecutive<V>(v);
+
+    if constexpr (B1 > 0) {
+        __syncthreads();                                       // everyone has read the raw staging area
+        exchange_write<L0, V>(xch, v, t);
+        __syncthreads();
+        exchange_read<L1, V>(xch, v, t);
+        butterfly_groups<L1, V>(v);
+    }
+    if constexpr (B2 > 0) {
+        __syncthreads();
+        exchange_write<L1, V>(xch, v, t);
+        __syncthreads();
+        exchange_read<L2, V>(xch, v, t);
+        butterfly_groups<L2, V>(v);
+    }
+    using LF = std::conditional_t<(B2 > 0), L2, std::conditional_t<(B1 > 0), L1, L0>>;
+    constexpr int C = LF::C;
+    constexpr int PIECE = C < 8 ? C : 8;                       // elements per store; dim % 8 == 0 so a piece never straddles dim
+
+    const float2 sc2 = make_float2(scale, scale);
+#pragma unroll
+    for (int i = 0; i < V; i += 2) {
+        const float2 m = fmul2(make_float2(v[i], v[i + 1]), sc2);
+        v[i] = m.x; v[i + 1] = m.y;
+    }
+
+    Tout* outr = out + row * (int64_t)dim;
+    if constexpr (EPI == Epilogue::Cast) {
+#pragma unroll
+        for (int j = 0; j < LF::G; ++j) {
+            const int e = LF::elem(t, j);
+#pragma unroll
+            for (int pc = 0; pc < C / PIECE; ++pc) {
+                if (row_ok && e + pc * PIECE < dim) {
+                    float o[PIECE];
+#pragma unroll
+                    for (int i = 0; i < PIECE; ++i) o[i] = v[j * C + pc * PIECE + i];
+                    store_elems<Tout, PIECE>(outr + e + pc * PIECE, o);
                 }
             }
-#pragma unroll
-            for (int i = 0; i < NB; ++i) fwht_regs<A>(w[i]);
         }
-
+    } else {
+        // round to the input dtype (what the unfused chain stores), then the row's absmax
         float amax = 0.f;
-        if (active) {
 #pragma unroll
-            for (int i = 0; i < NB; ++i)
+        for (int j = 0; j < LF::G; ++j) {
+            const bool in = LF::elem(t, j) < dim;              // dim % 8 == 0: a run of <= 8 is all in or all out
+            float m = 0.f;
 #pragma unroll
-                for (int a = 0; a < A; ++a) {
-                    w[i][a] = __fmul_rn(w[i][a], scale);
-                    if constexpr (EPI == Epilogue::Quant) {
-                        w[i][a] = round_through<Tin>(w[i][a]);
-                        if (a * 512 + b0 + i < dim) amax = fmaxf(amax, fabsf(w[i][a]));
-                    }
-                }
+            for (int i = 0; i < C; ++i) {
+                v[j * C + i] = round_through<Tin>(v[j * C + i]);
+                if (C <= 8 || LF::elem(t, j) + i < dim) m = fmaxf(m, fabsf(v[j * C + i]));
+            }
+            if (C > 8 || in) amax = fmaxf(amax, m);
         }
-        float qscale = 0.f;
-        bool zero_row = false;
-        if constexpr (EPI == Epilogue::Quant) {
-            amax = warp_max(amax);
-            if (lane == 0) red[warp] = amax;
+        // reduce over the T threads of the row
+#pragma unroll
+        for (int m = 1; m < (T < 32 ? T : 32); m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        if constexpr (T > 32) {
+            constexpr int WPR = T / 32;                        // warps per row
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
             __syncthreads();
-            amax = red[0];
+            amax = red[r_in_cta * WPR];
 #pragma unroll
-            for (int k = 1; k < A; ++k) amax = fmaxf(amax, red[k]);
-            const float qmax = std::is_same_v<Tout, int8_t> ? 127.0f : 448.0f;
-            qscale = __fdiv_rn(qmax, amax);
-            zero_row = amax == 0.f;
-            if (tid == 0) scales[row] = __fdiv_rn(1.0f, qscale);
+            for (int k = 1; k < WPR; ++k) amax = fmaxf(amax, red[r_in_cta * WPR + k]);
         }
-        if (active) {
+        const float qmax = std::is_same_v<Tout, int8_t> ? 127.0f : 448.0f;
+        const float qscale = __fdiv_rn(qmax, amax);
+        if (row_ok && t == 0) scales[row] = __fdiv_rn(1.0f, qscale);
+        const float qmul = amax == 0.f ? 0.f : qscale;         // an all-zero row quantises to zeros (0 * 0, not 0 * inf)
 #pragma unroll
-            for (int a = 0; a < A; ++a) {
-                const int e = a * 512 + b0;
-                if (e < dim) {                      // dim % 8 == 0 and NB <= 8: a chunk never straddles dim
-                    float o[NB];
+        for (int j = 0; j < LF::G; ++j) {
+            const int e = LF::elem(t, j);
 #pragma unroll
-                    for (int i = 0; i < NB; ++i) o[i] = w[i][a];
-                    if constexpr (EPI == Epilogue::Cast) store_elems<Tout, NB>(out + row * (int64_t)dim + e, o);
-                    else store_quant<Tout, NB>(out + row * (int64_t)dim + e, o, qscale, zero_row);
+            for (int pc = 0; pc < C / PIECE; ++pc) {
+                if (row_ok && e + pc * PIECE < dim) {
+                    using BV = typename ByteVec<PIECE>::type;
+                    union { BV vec; uint8_t b[PIECE]; } u;
+#pragma unroll
+                    for (int i = 0; i < PIECE; ++i)
+                        u.b[i] = quantize_fast<Tout>(__fmul_rn(v[j * C + pc * PIECE + i], qmul));
+                    *reinterpret_cast<BV*>(reinterpret_cast<uint8_t*>(outr) + e + pc * PIECE) = u.vec;
                 }
             }
         }
@@ -293,18 +436,27 @@ static int launch_hadamard(const void* x, void* out, float* scales, int64_t rows
         switch (log_g) { Q8K_HS(0); Q8K_HS(1); Q8K_HS(2); Q8K_HS(3); Q8K_HS(4); Q8K_HS(5); }
 #undef Q8K_HS
     } else {
-        const int log_a = log_n - 9;
-        if (log_a > 5) { set_error_detail("%s: dim %d exceeds 16384", op, dim); return Q8K_ERR_UNSUPPORTED; }
-        const size_t smem = (size_t)(512 << log_a) * sizeof(float);
-#define Q8K_HL(LA)                                                                                        \
-    case LA: {                                                                                            \
-        auto kern = hadamard_large_kernel<Tin, Tout, LA, EPI>;                                            \
+        if (log_n > 14) { set_error_detail("%s: dim %d exceeds 16384", op, dim); return Q8K_ERR_UNSUPPORTED; }
+#define Q8K_HR(LN, LV, NR)                                                                                \
+    case LN: {                                                                                            \
+        auto kern = hadamard_row_kernel<Tin, Tout, LN, LV, NR, EPI>;                                      \
+        constexpr int smem = NR * (1 << LN) * (int)sizeof(float);                                         \
         if (smem > 48 * 1024)                                                                             \
-            Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        kern<<<(unsigned)rows, 32 << LA, (LA == 0 ? 0 : smem), st>>>(xi, o, scales, dim, stride, scale);    \
+            Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));   \
+        kern<<<(unsigned)((rows + NR - 1) / NR), NR << (LN - LV), smem, st>>>(xi, o, scales, rows, dim, stride, scale); \
     } break
-        switch (log_a) { Q8K_HL(0); Q8K_HL(1); Q8K_HL(2); Q8K_HL(3); Q8K_HL(4); Q8K_HL(5); }
-#undef Q8K_HL
+        // (row length, values per thread, rows per CTA), chosen by measurement: the plain transform
+        // likes more values per thread (fewer exchanges), the fused quantizer more threads
+        if constexpr (EPI == Epilogue::Cast) {
+            switch (log_n) {
+                Q8K_HR(9, 5, 8); Q8K_HR(10, 6, 8); Q8K_HR(11, 6, 4); Q8K_HR(12, 6, 2); Q8K_HR(13, 6, 1); Q8K_HR(14, 7, 1);
+            }
+        } else {
+            switch (log_n) {
+                Q8K_HR(9, 5, 8); Q8K_HR(10, 5, 4); Q8K_HR(11, 5, 2); Q8K_HR(12, 6, 2); Q8K_HR(13, 6, 1); Q8K_HR(14, 7, 1);
+            }
+        }
+#undef Q8K_HR
     }
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;

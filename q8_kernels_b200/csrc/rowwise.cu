@@ -87,7 +87,8 @@ tokenwise_quant_kernel(const Tin* __restrict__ x, Tout* __restrict__ q, float* _
             for (int j = 0; j < kItem; ++j) {
                 const float y = zero_row ? 0.f : __fmul_rn(v[i][j], scale);
                 if constexpr (kInt8) {
-                    o.b[j] = (uint8_t)(int8_t)(int)roundf(y);      // round half away from zero
+                    // exact round half away from zero: truncate y + copysign(0.5 - 2^-25, y)
+                    o.b[j] = (uint8_t)(int8_t)__float2int_rz(__fadd_rn(y, copysignf(0.49999997f, y)));
                 } else {
                     o.b[j] = float_to_e4m3_c10(y);
                 }

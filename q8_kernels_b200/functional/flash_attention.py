@@ -21,10 +21,11 @@ def is_16bit(x) -> bool:
 
 def flash_attn_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: Optional[float] = None,
                     batch_mask: Optional[torch.Tensor] = None, apply_qk_hadamard: bool = False,
-                    out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                    out_dtype: Optional[torch.dtype] = None, token_major_out: bool = False) -> torch.Tensor:
     """q [B,H,Sq,D], k,v [B,H,Skv,D] (views allowed); ``batch_mask`` is int32 [B]
     with the number of valid keys per batch entry.  Returns [B,H,Sq,D] in e4m3
-    (the reference's output dtype) unless ``out_dtype=torch.bfloat16``."""
+    (the reference's output dtype) unless ``out_dtype=torch.bfloat16``.  With ``token_major_out``
+    the same values are stored as [B,Sq,H,D] and the [B,H,Sq,D] view of that buffer is returned."""
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
     assert batch_mask is None or (batch_mask.shape[0] == q.shape[0] and batch_mask.ndim == 1)
@@ -38,7 +39,7 @@ def flash_attn_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_s
         else:
             qk_scale, kernel_scale = 1.0, softmax_scale
         q8, k8, vt8 = native.attention_prep(q, k, v, apply_qk_hadamard, qk_scale)
-        return native.flash_attention(q8, k8, vt8, kernel_scale, batch_mask, out_dtype)
+        return native.flash_attention(q8, k8, vt8, kernel_scale, batch_mask, out_dtype, token_major_out)
 
     # general path, same steps as the reference
     if head_size_og % 32 != 0:

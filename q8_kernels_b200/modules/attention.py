@@ -7,12 +7,14 @@ Hadamard kernel then rejects), and ``head_shard=(rank, world)`` lets a caller
 run the attention core on a slice of the heads (the q/k norm spans all heads, so
 slicing happens after norm and RoPE); the caller gathers the slices.
 """
+import math
 from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
 
 from .. import functional as Q8F
+from .. import native
 from .linear import Q8Linear
 from .rms_norm import RMSNorm
 
@@ -40,6 +42,17 @@ class Attention(nn.Module):
         self.to_v = Q8Linear(kv_dim, self.inner_dim, bias=bias)
         self.to_out = Q8Linear(self.inner_dim, out_dim, out_bias)
 
+    @staticmethod
+    def _quantize_once(x):
+        """Hadamard (scale 1/sqrt(K)) + per-token INT8 quantizer of an activation, as q8_linear
+        applies to a 16-bit / e4m3 input; already-quantised inputs pass through."""
+        if x.dtype == torch.int8:
+            raise ValueError("Attention expects un-quantised activations")
+        if x.dtype == torch.float16:
+            x = x.to(torch.bfloat16)
+        q, s = native.hadamard_quant(x, 1 / math.sqrt(x.shape[-1]), torch.int8)
+        return q, s
+
     def forward(self, hidden_states, freqs_cis=None, encoder_hidden_states=None, attention_mask=None,
                 non_mm_precision=torch.bfloat16, mm_out_dtype=None, apply_qk_hadamard=True, attn_type="torch",
                 head_shard: Optional[Tuple[int, int]] = None, gather_heads=None):
@@ -48,14 +61,22 @@ class Attention(nn.Module):
             if attention_mask.ndim == 0:
                 attention_mask = attention_mask.reshape(1)
 
-        query = self.to_q(hidden_states, out_dtype=mm_out_dtype)
+        # The reference quantises the same activation once per projection (q8_linear re-runs
+        # Hadamard + quantizer on every call); here each distinct input is quantised once and the
+        # int8 rows + scales are shared, which is bit-identical.
+        kv_src = encoder_hidden_states if encoder_hidden_states is not None else hidden_states
+        hq, hs = self._quantize_once(hidden_states)
+        if encoder_hidden_states is not None:
+            kq, ks = self._quantize_once(kv_src)
+        else:
+            kq, ks = hq, hs
+        query = self.to_q(hq, hs, out_dtype=mm_out_dtype)
         if self.qk_rms_norm:
             query = self.q_norm(query, non_mm_precision)
-        kv_src = encoder_hidden_states if encoder_hidden_states is not None else hidden_states
-        key = self.to_k(kv_src, out_dtype=mm_out_dtype)
+        key = self.to_k(kq, ks, out_dtype=mm_out_dtype)
         if self.qk_rms_norm:
             key = self.k_norm(key, non_mm_precision)
-        value = self.to_v(kv_src, out_dtype=mm_out_dtype)
+        value = self.to_v(kq, ks, out_dtype=mm_out_dtype)
         if encoder_hidden_states is None and self.use_rope:
             query = Q8F.rope.apply_rope(query, freqs_cis[0], freqs_cis[1], out_type=non_mm_precision)
             key = Q8F.rope.apply_rope(key, freqs_cis[0], freqs_cis[1], out_type=non_mm_precision)
@@ -73,8 +94,10 @@ class Attention(nn.Module):
             heads = per
 
         if attn_type == "q8_kernels":
+            # stored token-major, so the transpose + reshape + contiguous below is a free view
             hidden_states = Q8F.flash_attention.flash_attn_func(query, key, value, batch_mask=attention_mask,
-                                                                apply_qk_hadamard=apply_qk_hadamard)
+                                                                apply_qk_hadamard=apply_qk_hadamard,
+                                                                token_major_out=True)
         elif attn_type == "torch":
             query = query.to(non_mm_precision)
             key = key.to(non_mm_precision)

@@ -240,10 +240,12 @@ def fp8_mm_bias(a, b, bias, a_scales, b_scales, fuse_gelu: bool, out_type: Optio
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,
                     batch_mask: Optional[torch.Tensor] = None,
-                    out_type: Optional[torch.dtype] = None) -> torch.Tensor:
+                    out_type: Optional[torch.dtype] = None, token_major_out: bool = False) -> torch.Tensor:
     """csrc/flash_attention/flash_attention.cpp:18-48: q [B,H,M,64], k [B,H,N,64],
     v [B,H,64,ceil16(N)] e4m3, optional int32 [B] valid-key counts; the output is
-    e4m3 [B,H,M,64] like the reference unless ``out_type`` asks for bfloat16."""
+    e4m3 [B,H,M,64] like the reference unless ``out_type`` asks for bfloat16.
+    ``token_major_out`` stores the result as [B,M,H,64] and returns its [B,H,M,64] view, so the
+    caller's ``transpose(1,2).reshape(B,M,H*64)`` is free."""
     dev = require_cuda(q, k, v, batch_mask)
     if q.dtype != E4M3 or k.dtype != E4M3 or v.dtype != E4M3:
         raise Q8KernelError("flash_attention: q, k, v must be float8_e4m3fn")
@@ -264,12 +266,17 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_s
         batch_mask = batch_mask.contiguous()
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     out_type = E4M3 if out_type is None else out_type
-    out = torch.empty((B, H, M, 64), dtype=out_type, device=dev)
+    if token_major_out:
+        buf = torch.empty((B, M, H, 64), dtype=out_type, device=dev)
+        strides = (M * H * 64, 64, H * 64)
+    else:
+        buf = torch.empty((B, H, M, 64), dtype=out_type, device=dev)
+        strides = (H * M * 64, M * 64, 64)
     with torch.cuda.device(dev):
-        check(lib.q8k_flash_attention(ptr(q), ptr(k), ptr(v), ptr(out), dt(out_type), B, H, M, N,
-                                      float(softmax_scale), ptr(batch_mask), ptr(_lib.status_word(dev)),
-                                      stream_ptr(dev)), "flash_attention")
-    return out
+        check(lib.q8k_flash_attention_strided(ptr(q), ptr(k), ptr(v), ptr(buf), dt(out_type), B, H, M, N, *strides,
+                                              float(softmax_scale), ptr(batch_mask), ptr(_lib.status_word(dev)),
+                                              stream_ptr(dev)), "flash_attention")
+    return buf.transpose(1, 2) if token_major_out else buf
 
 
 def attention_prep(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, apply_hadamard: bool,

@@ -18,7 +18,7 @@ import torch
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("case", choices=["gemm_fp8", "gemm_int8", "attention", "cross_attention", "quantizer", "hadamard",
-                                     "hadamard_quant", "rms_norm", "rope", "gelu"])
+                                     "hadamard_quant", "rms_norm", "rope", "gelu", "dit_block"])
     ap.add_argument("--m", type=int, default=6144)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--n", type=int, default=2048)
@@ -62,6 +62,21 @@ def main() -> None:
             lens = torch.randint(16, 129, (a.b,), generator=g, device=dev, dtype=torch.int32)
         fn = lambda: nat.flash_attention(q8_, k8_, vt_, 1.0, lens, torch.bfloat16)  # noqa: E731
         work = 4.0 * a.b * a.h * a.s * skv * 64 / 1e12
+    elif a.case == "dit_block":
+        # one LTX-Video block (hidden 2048, 32 x 64 heads, FFN 8192) on --s tokens and 128 text tokens
+        cfg = q8.blocks.LTXStackConfig(num_layers=1)
+        stack = q8.blocks.random_init_(q8.blocks.LTXStack(cfg), seed=1, device=dev)
+        blk = stack.transformer_blocks[0]
+        S, T = a.s, 128
+        x = torch.randn(a.b, S, cfg.inner_dim, generator=g, device=dev).to(torch.bfloat16)
+        text = torch.randn(a.b, T, cfg.inner_dim, generator=g, device=dev).to(torch.bfloat16)
+        ts = (torch.randn(a.b, 1, 6 * cfg.inner_dim, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+        freqs = stack.freqs_cis(q8.blocks.latent_grid(S // 384, 16, 24, device=dev))
+        lens = torch.full((a.b,), 97, dtype=torch.int32, device=dev)
+        def fn():
+            with torch.no_grad():
+                return blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels")
+        work = a.b * (2.0 * S * (6 * 2048 ** 2 + 2 * 2048 * 8192) + 4.0 * 2048 ** 2 * T + 4.0 * 32 * S * (S + T) * 64) / 1e12
     else:
         x = torch.randn(a.rows, a.dim, generator=g, device=dev).to(torch.bfloat16)
         unit = "GB/s"

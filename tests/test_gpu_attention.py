@@ -120,3 +120,14 @@ def test_self_attention_dit_shape_sampled(nat, cuda_device):
     # so peaky rows lose some tail mass -- never gain more than one e4m3 ulp
     assert out.max().item() <= 0.75 * (1 + 2 ** -4)
     assert (out - 0.75).abs().mean().item() < 0.03 and out.min().item() > 0.5
+
+
+def test_token_major_output_is_the_same_values(nat, cuda_device):
+    q8, k8, vt, ks = _fp8_operands(2, 4, 200, 333, seed=17)
+    d = cuda_device
+    a = nat.flash_attention(q8.to(d), k8.to(d), vt.to(d), ks, None, torch.bfloat16)
+    b = nat.flash_attention(q8.to(d), k8.to(d), vt.to(d), ks, None, torch.bfloat16, token_major_out=True)
+    assert b.shape == a.shape and not b.is_contiguous()
+    assert torch.equal(a, b)
+    flat = b.transpose(1, 2).reshape(2, 200, 4 * 64)
+    assert flat.data_ptr() == b.data_ptr()                     # the module's reshape is a view, not a copy
