@@ -18,7 +18,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libq8k_b200.so")
 
-SOURCES = ["capi.cu", "rowwise.cu", "hadamard.cu", "gemm.cu", "attention.cu"]
+SOURCES = ["capi.cu", "rowwise.cu", "hadamard.cu", "gemm.cu", "gemm_pair.cu", "attention.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

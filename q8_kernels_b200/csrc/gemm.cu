@@ -19,27 +19,11 @@
 // reference: float(acc) * (sa*sb) + bias, optional tanh-GELU, then bf16 (RNE)
 // or e4m3 (saturating).
 
-#include "common.cuh"
-#include "tcgen05.cuh"
-#include "tensormap.cuh"
+#include <stdlib.h>
+
+#include "gemm_common.cuh"
 
 namespace q8k {
-
-constexpr int kGemmBM = 128;
-constexpr int kGemmBK = 128;          // bytes == elements along K per stage
-constexpr int kGemmEpilogueThreads = 256;
-constexpr int kGemmThreads = 64 + kGemmEpilogueThreads;
-
-struct GemmParams {
-    const float* a_scales;
-    const float* b_scales;
-    const float* bias;
-    void* out;
-    int* status;
-    int M, N, K;
-    int batch_a, batch_b;             // 1 when that operand carries a batch dim
-    int m_tiles, n_tiles, total_tiles;
-};
 
 template <int BN, int STAGES>
 struct GemmSmem {
@@ -57,14 +41,6 @@ struct GemmSmem {
     static constexpr int kTotal = kBiasOffset + BN * 4;
     static constexpr int kDynamic = kTotal + 1024;          // slack to align the base to 1024 B
 };
-
-__device__ __forceinline__ float gelu_tanh_fast(float y) {
-    // tanh.approx has ~2^-11 absolute error, far below the bf16 / e4m3 output step.
-    const float u = 0.7978845608028654f * fmaf(0.044715f * y * y, y, y);
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-    return 0.5f * y * (1.0f + t);
-}
 
 template <bool INT8, int BN, int STAGES, bool GELU, bool OUT_E4M3>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -302,7 +278,7 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // ------------------------------------------------------------------ host side
 static int g_num_sms = 0;
 
-static int num_sms() {
+int gemm_num_sms() {
     if (g_num_sms == 0) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess) return 148;
@@ -318,7 +294,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     using L = GemmSmem<BN, STAGES>;
     auto kern = gemm_8bit_kernel<INT8, BN, STAGES, GELU, OUT_E4M3>;
     Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
-    const int grid = p.total_tiles < num_sms() ? p.total_tiles : num_sms();
+    const int grid = p.total_tiles < gemm_num_sms() ? p.total_tiles : gemm_num_sms();
     kern<<<grid, kGemmThreads, L::kDynamic, st>>>(ta, tb, p);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
@@ -375,6 +351,14 @@ static int gemm_8bit(bool int8, const void* a, const void* b, const float* bias,
     cudaStream_t st = (cudaStream_t)stream;
     const bool gelu = fuse_gelu != 0;
     const bool e4m3 = out_dtype == Q8K_DT_E4M3;
+
+    // Large problems run on 256 x 256 tiles owned by CTA pairs (half the B-operand shared-memory
+    // traffic per CTA); small ones, or devices that cannot co-schedule the pairs, on 128 x 256 tiles.
+    static const bool pair_disabled = getenv("Q8K_GEMM_NO_PAIR") != nullptr;
+    if (!pair_disabled && M > kGemmBM && N > 128) {
+        const int rc = launch_gemm_pair(int8, gelu, e4m3, a, b, p, bs_a, bs_b, st);
+        if (rc != Q8K_ERR_UNSUPPORTED) return rc;
+    }
 #define Q8K_GEMM_DISPATCH(I8, BNV, ST)                                                        \
     do {                                                                                      \
         if (gelu) return e4m3 ? launch_gemm<I8, BNV, ST, true, true>(ta, tb, p, st)           \

@@ -1,0 +1,42 @@
+// Pieces shared by the single-CTA and the CTA-pair 8-bit GEMM kernels.
+#pragma once
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+#include "tensormap.cuh"
+
+namespace q8k {
+
+constexpr int kGemmBM = 128;
+constexpr int kGemmBK = 128;          // bytes == elements along K per stage
+constexpr int kGemmEpilogueThreads = 256;
+constexpr int kGemmThreads = 64 + kGemmEpilogueThreads;
+
+struct GemmParams {
+    const float* a_scales;
+    const float* b_scales;
+    const float* bias;
+    void* out;
+    int* status;
+    int M, N, K;
+    int batch_a, batch_b;             // 1 when that operand carries a batch dim
+    int m_tiles, n_tiles, total_tiles;
+};
+
+__device__ __forceinline__ float gelu_tanh_fast(float y) {
+    // tanh.approx has ~2^-11 absolute error, far below the bf16 / e4m3 output step.
+    const float u = 0.7978845608028654f * fmaf(0.044715f * y * y, y, y);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+    return 0.5f * y * (1.0f + t);
+}
+
+int gemm_num_sms();
+
+// CTA-pair (cta_group::2) variant: 256 x 256 output tiles per cluster of two CTAs.  Returns
+// Q8K_ERR_UNSUPPORTED (without touching the error detail) when the device cannot co-schedule
+// the clusters, in which case the caller falls back to the single-CTA kernel.
+int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, const void* a, const void* b, const GemmParams& p,
+                     int bs_a, int bs_b, cudaStream_t st);
+
+}  // namespace q8k

@@ -1,0 +1,355 @@
+// CTA-pair variant of the 8-bit GEMM: a cluster of two CTAs on neighbouring SMs owns a 256 x 256
+// output tile and runs ONE tcgen05.mma (cta_group::2, M = 256, N = 256, K = 32) per K slice.
+//
+// Why: in the single-CTA kernel every MMA streams a 128-row A slab and a 256-row B slab out of the
+// CTA's shared memory, and TMA writes the same 48 KB per stage into it; shared memory bandwidth is
+// what caps the main loop.  In a pair each CTA holds its own 128 rows of A and only HALF of the B
+// rows (128 of 256), so both the TMA fill and the tensor-core reads per CTA drop by a third while
+// the pair produces twice the output.
+//
+// Roles per CTA (10 warps, same as the single-CTA kernel):
+//   warp 0     TMA producer: its A rows and its half of the B rows, 32 KB per stage, 6 stages; the
+//              transaction bytes of BOTH CTAs are credited to the leader CTA's "full" barrier
+//   warp 1     TMEM allocation (both CTAs); in the leader (even rank) one thread issues the MMAs
+//              and commits to the "empty" / "accumulator full" barriers of both CTAs
+//   warps 2-9  epilogue of the CTA's own 128 rows x 256 columns (identical arithmetic to the
+//              single-CTA kernel); "accumulator free" arrivals of both CTAs go to the leader
+// No multicast loads are used: every CTA fetches its own operand tiles with plain TMA loads.
+
+#include "gemm_common.cuh"
+
+namespace q8k {
+
+constexpr int kPairBN = 256;                 // tile columns (128 B rows from each CTA)
+constexpr int kPairStages = 6;
+constexpr int kPairTmemCols = 512;           // two 256-column accumulators per CTA
+
+struct PairSmem {
+    static constexpr int kABytes = kGemmBM * kGemmBK;              // 16 KB: this CTA's 128 rows of A
+    static constexpr int kBBytes = (kPairBN / 2) * kGemmBK;        // 16 KB: this CTA's 128 rows of B
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarOffset = kPairStages * kStageBytes;
+    static constexpr int kNumBars = 2 * kPairStages + 4;
+    static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
+    static constexpr int kAbortOffset = kTmemPtrOffset + 4;
+    static constexpr int kColScaleOffset = (kAbortOffset + 4 + 15) & ~15;
+    static constexpr int kBiasOffset = kColScaleOffset + kPairBN * 4;
+    static constexpr int kTotal = kBiasOffset + kPairBN * 4;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+struct PairParams {
+    GemmParams g;
+    int m_tiles2;                            // 256-row tiles per batch entry
+    int n_tiles2;
+    int total_tiles2;
+};
+
+template <bool INT8, bool GELU, bool OUT_E4M3>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const PairParams pp) {
+    using L = PairSmem;
+    const GemmParams& p = pp.g;
+    constexpr uint32_t IDESC = INT8 ? ptx::make_idesc_s8(2 * kGemmBM, kPairBN) : ptx::make_idesc_e4m3(2 * kGemmBM, kPairBN);
+
+    extern __shared__ uint8_t smem_raw[];
+    // the dynamic shared window starts at the same offset in both CTAs, so rounding up keeps the two layouts congruent
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t smem_base = ptx::smem_u32(smem);
+    const uint32_t bar_base = smem_base + L::kBarOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
+    auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + a); };
+    auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + 2 + a); };
+    volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
+    float* col_scale_smem = reinterpret_cast<float*>(smem + L::kColScaleOffset);
+    float* bias_smem = reinterpret_cast<float*>(smem + L::kBiasOffset);
+
+    const uint32_t rank = ptx::cluster_ctarank();              // 0 = leader, 1 = peer
+    const bool leader = rank == 0;
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int k_iters = (p.K + kGemmBK - 1) / kGemmBK;
+
+    // A launch that follows a failed one on the same status word does nothing.  The leader reads
+    // the word and hands its decision to the peer, so the two CTAs of a pair always agree.
+    __shared__ int prior_failure;
+    if (threadIdx.x == 0 && leader) {
+        const int v = p.status != nullptr ? *reinterpret_cast<volatile int*>(p.status) : 0;
+        prior_failure = v;
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(ptx::mapa_shared(ptx::smem_u32(&prior_failure), 1)), "r"(v)
+                     : "memory");
+    }
+    ptx::cluster_sync_all();
+    const bool skip = prior_failure != 0;
+    if (skip) return;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            ptx::mbar_init(full_bar(s), 2);                    // one arrive.expect_tx from each CTA's producer
+            ptx::mbar_init(empty_bar(s), 1);                   // one commit from the leader's MMA thread
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(tmem_full_bar(a), 1);
+            ptx::mbar_init(tmem_empty_bar(a), 2 * (kGemmEpilogueThreads / 32));   // every epilogue warp of both CTAs
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair<kPairTmemCols>(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)));
+        ptx::tmem_relinquish_alloc_permit_pair();
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync_all();                                   // both CTAs' barriers exist before anyone signals across
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    // barriers of the leader CTA, as seen from this CTA
+    auto leader_full_bar = [&](int s) { return ptx::mapa_shared(full_bar(s), 0); };
+    auto leader_tmem_empty_bar = [&](int a) { return ptx::mapa_shared(tmem_empty_bar(a), 0); };
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = cluster_id; ok && tile < pp.total_tiles2; tile += num_clusters) {
+                const int n_blk = tile % pp.n_tiles2;
+                const int m_blk = (tile / pp.n_tiles2) % pp.m_tiles2;
+                const int batch = tile / (pp.n_tiles2 * pp.m_tiles2);
+                const int a_row = (p.batch_a ? batch * p.M : 0) + m_blk * 2 * kGemmBM + (int)rank * kGemmBM;
+                const int b_row = (p.batch_b ? batch * p.N : 0) + n_blk * kPairBN + (int)rank * (kPairBN / 2);
+                for (int kb = 0; kb < k_iters; ++kb, ++it) {
+                    const int s = it % kPairStages;
+                    const uint32_t ph = (it / kPairStages) & 1u;
+                    if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t fb = leader_full_bar(s);
+                    ptx::mbar_arrive_expect_tx_cluster(fb, L::kStageBytes);
+                    const uint32_t a_dst = smem_base + s * L::kStageBytes;
+                    ptx::tma_load_2d_pair(a_dst, &tmap_a, fb, kb * kGemmBK, a_row);
+                    ptx::tma_load_2d_pair(a_dst + L::kABytes, &tmap_b, fb, kb * kGemmBK, b_row);
+                }
+            }
+            if (!ok && p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (8 << 8));
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            uint32_t it = 0;
+            uint32_t tile_i = 0;
+            bool ok = true;
+            for (int tile = cluster_id; ok && tile < pp.total_tiles2; tile += num_clusters, ++tile_i) {
+                const uint32_t acc = tile_i & 1u;
+                const uint32_t acc_ph = (tile_i >> 1) & 1u;
+                if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
+                ptx::tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kPairBN;
+                for (int kb = 0; kb < k_iters; ++kb, ++it) {
+                    const int s = it % kPairStages;
+                    const uint32_t ph = (it / kPairStages) & 1u;
+                    if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+                    ptx::tcgen05_fence_after_sync();
+                    const uint32_t a_addr = smem_base + s * L::kStageBytes;
+                    const uint64_t a_desc = ptx::make_kmajor_desc(a_addr, 128);
+                    const uint64_t b_desc = ptx::make_kmajor_desc(a_addr + L::kABytes, 128);
+#pragma unroll
+                    for (int k = 0; k < kGemmBK / 32; ++k) {
+                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        if constexpr (INT8) ptx::mma_i8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, accumulate);
+                        else ptx::mma_f8f6f4_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, accumulate);
+                    }
+                    // the stage is reusable in BOTH CTAs once these MMAs retire
+                    ptx::tcgen05_commit_pair(ptx::mapa_shared(empty_bar(s), 0));
+                    ptx::tcgen05_commit_pair(ptx::mapa_shared(empty_bar(s), 1));
+                }
+                if (ok) {
+                    ptx::tcgen05_commit_pair(ptx::mapa_shared(tmem_full_bar(acc), 0));
+                    ptx::tcgen05_commit_pair(ptx::mapa_shared(tmem_full_bar(acc), 1));
+                }
+            }
+            if (!ok && p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (9 << 8));
+        }
+    } else {
+        // ------------------------------------------------ epilogue (warps 2..9) of this CTA's 128 rows
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int epi_tid = threadIdx.x - 64;
+        constexpr int HALF_COLS = kPairBN / 2;
+        constexpr int NCH = HALF_COLS / 32;
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < pp.total_tiles2; tile += num_clusters, ++tile_i) {
+            const int n_blk = tile % pp.n_tiles2;
+            const int m_blk = (tile / pp.n_tiles2) % pp.m_tiles2;
+            const int batch = tile / (pp.n_tiles2 * pp.m_tiles2);
+            const int n0 = n_blk * kPairBN;
+            const uint32_t acc = tile_i & 1u;
+            const uint32_t acc_ph = (tile_i >> 1) & 1u;
+
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            for (int c = epi_tid; c < kPairBN; c += kGemmEpilogueThreads) {
+                const int n = n0 + c;
+                const bool in = n < p.N;
+                col_scale_smem[c] = in ? p.b_scales[(p.batch_b ? (int64_t)batch * p.N : 0) + n] : 0.f;
+                bias_smem[c] = (in && p.bias != nullptr) ? p.bias[n] : 0.f;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+
+            if (ok) ok = ptx::mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) continue;
+            ptx::tcgen05_fence_after_sync();
+
+            const int row = m_blk * 2 * kGemmBM + (int)rank * kGemmBM + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+            const float sa = row_ok ? p.a_scales[(p.batch_a ? (int64_t)batch * p.M : 0) + row] : 0.f;
+            const int64_t out_row = ((int64_t)batch * p.M + row) * p.N;
+            const int col_base = half * HALF_COLS;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kPairBN + col_base;
+
+            uint32_t r[2][32];
+            __syncwarp();
+            ptx::tmem_ld_32x32b_x32(t_row, r[0]);
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                ptx::tmem_wait_ld();
+                if (c + 1 < NCH) ptx::tmem_ld_32x32b_x32(t_row + (c + 1) * 32, r[(c + 1) & 1]);
+                const int cl = col_base + c * 32;
+                const int nc = n0 + cl;
+                if (row_ok && nc < p.N) {
+                    const uint32_t(&rc)[32] = r[c & 1];
+                    float y[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float accf = INT8 ? (float)(int)rc[j] : __uint_as_float(rc[j]);
+                        float v = fmaf(accf, sa * col_scale_smem[cl + j], bias_smem[cl + j]);
+                        if constexpr (GELU) v = gelu_tanh_fast(v);
+                        y[j] = v;
+                    }
+                    const int valid = min(32, p.N - nc);
+                    if constexpr (OUT_E4M3) {
+                        uint8_t* o = reinterpret_cast<uint8_t*>(p.out) + out_row + nc;
+#pragma unroll
+                        for (int v4 = 0; v4 < 2; ++v4) {
+                            if (v4 * 16 < valid) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const int j = v4 * 16 + q * 4;
+                                    w[q] = (uint32_t)float2_to_e4m3x2_sat(y[j], y[j + 1]) |
+                                           ((uint32_t)float2_to_e4m3x2_sat(y[j + 2], y[j + 3]) << 16);
+                                }
+                                reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    } else {
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + out_row + nc;
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4) {
+                            if (v4 * 8 < valid) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const int j = v4 * 8 + q * 2;
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(y[j], y[j + 1]);
+                                    w[q] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
+                                reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            ptx::tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(leader_tmem_empty_bar(acc));   // the leader's MMA thread waits for both CTAs
+        }
+        if (!ok && p.status != nullptr && epi_tid == 0) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (10 << 8));
+    }
+
+    // ---------------------------------------------------- teardown: neither CTA may leave while the other can
+    // still read its shared memory, signal its barriers or write its TMEM
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync_all();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc_pair<kPairTmemCols>(tmem_base);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+template <bool INT8, bool GELU, bool OUT_E4M3>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const PairParams& pp, cudaStream_t st) {
+    auto kern = gemm_8bit_pair_kernel<INT8, GELU, OUT_E4M3>;
+    Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamic));
+    // how many 2-CTA clusters can be resident at once (cached per kernel variant)
+    static int max_clusters = -1;
+    if (max_clusters < 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * gemm_num_sms());
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = PairSmem::kDynamic;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        max_clusters = n;
+    }
+    if (max_clusters < 8) return Q8K_ERR_UNSUPPORTED;
+    const int clusters = pp.total_tiles2 < max_clusters ? pp.total_tiles2 : max_clusters;
+    kern<<<2 * clusters, kGemmThreads, PairSmem::kDynamic, st>>>(ta, tb, pp);
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, const void* a, const void* b, const GemmParams& p,
+                     int bs_a, int bs_b, cudaStream_t st) {
+    const char* op = int8 ? "q8_mm" : "fp8_mm";
+    CUtensorMap ta, tb;
+    {
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)bs_a * (uint64_t)p.M};
+        const uint64_t strides[1] = {(uint64_t)p.K};
+        const uint32_t box[2] = {(uint32_t)kGemmBK, (uint32_t)kGemmBM};
+        if (int rc = make_byte_tensor_map(&ta, a, 2, dims, strides, box, 128, op)) return rc;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)bs_b * (uint64_t)p.N};
+        const uint64_t strides[1] = {(uint64_t)p.K};
+        const uint32_t box[2] = {(uint32_t)kGemmBK, (uint32_t)(kPairBN / 2)};
+        if (int rc = make_byte_tensor_map(&tb, b, 2, dims, strides, box, 128, op)) return rc;
+    }
+    PairParams pp;
+    pp.g = p;
+    const int batch = bs_a > bs_b ? bs_a : bs_b;
+    pp.m_tiles2 = (p.M + 2 * kGemmBM - 1) / (2 * kGemmBM);
+    pp.n_tiles2 = (p.N + kPairBN - 1) / kPairBN;
+    const int64_t total = (int64_t)pp.m_tiles2 * pp.n_tiles2 * batch;
+    if (total > 0x7fffffffLL) return Q8K_ERR_UNSUPPORTED;
+    pp.total_tiles2 = (int)total;
+#define Q8K_PAIR(I8)                                                                  \
+    do {                                                                              \
+        if (gelu) return out_e4m3 ? launch_pair<I8, true, true>(ta, tb, pp, st)       \
+                                  : launch_pair<I8, true, false>(ta, tb, pp, st);     \
+        return out_e4m3 ? launch_pair<I8, false, true>(ta, tb, pp, st)                \
+                        : launch_pair<I8, false, false>(ta, tb, pp, st);              \
+    } while (0)
+    if (int8) Q8K_PAIR(true);
+    Q8K_PAIR(false);
+#undef Q8K_PAIR
+}
+
+}  // namespace q8k
