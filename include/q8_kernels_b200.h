@@ -81,6 +81,16 @@ Q8K_API int q8k_fast_hadamard_transform(const void* x, int x_dtype, void* out, i
 Q8K_API int q8k_hadamard_quant(const void* x, int x_dtype, void* q, int q_dtype, float* scales,
                        int64_t rows, int dim, int64_t x_row_stride, float scale, void* stream);
 
+/* The whole pre-linear chain of an LTX block in one pass over x: RMS norm without affine weight,
+ * adaLN modulation n*(1+s)+h with per-batch bf16 rows s, h ([rows/rows_per_mod, dim]), Hadamard
+ * (times `scale`) and the per-row quantizer, with the bf16 roundings of the separate ops
+ * (q8_kernels/blocks/ltx_transformer_block.py:38-39,53-54 followed by functional/linear.py:30-31).
+ * x bf16 [rows, dim] contiguous, dim in (256, 8192], a multiple of 16.  Equal to the unfused chain
+ * up to the fp32 summation order of the mean square (a row's 1/rms may differ by one ulp).        */
+Q8K_API int q8k_norm_modulate_quant(const void* x, const void* mod_scale, const void* mod_shift, void* q, int q_dtype,
+                            float* scales, int64_t rows, int dim, int64_t rows_per_mod, float scale,
+                            void* stream);
+
 /* RMS norm without eps: r = rsqrt(mean(x^2)), out = (x*r)*w (w fp32 or NULL),
  * rrms[rows] = r (may be NULL).  x, out bf16|e4m3; dim a multiple of 16.
  * Replaces rms_norm: csrc/ops/rms_norm.cpp:103-154, rms_norm_cuda.cu:100-171. */
@@ -119,6 +129,17 @@ Q8K_API int q8k_q8_mm(const void* a, const void* b, const float* bias, const flo
 Q8K_API int q8k_fp8_mm(const void* a, const void* b, const float* bias, const float* a_scales,
                const float* b_scales, void* out, int out_dtype, int bs_a, int bs_b,
                int M, int N, int K, int fuse_gelu, int* dev_status, void* stream);
+
+/* GEMM with the block's gated residual folded into the epilogue:
+ *   out[m,n] = bf16( bf16( gate[m / rows_per_gate, n] * bf16(y[m,n]) ) + resid[m,n] ),  y = (A.B^T)*(sa*sb) + bias
+ * gate (bf16, [ceil(rows/rows_per_gate), N], may be NULL for a plain residual add) and resid (bf16,
+ * [batch*M, N]) follow the roundings of the separate torch ops they replace
+ * (`gate_msa * attn_output + hidden_states`, q8_kernels/blocks/ltx_transformer_block.py:41,52,56),
+ * so the result is bit-identical to q8_mm_bias followed by those ops.  int8 != 0 selects INT8
+ * operands, else e4m3.  Output bf16 [max(bs_a,bs_b), M, N].                                        */
+Q8K_API int q8k_mm_gate_residual(int int8, const void* a, const void* b, const float* bias, const float* a_scales,
+                         const float* b_scales, const void* gate, const void* resid, int64_t rows_per_gate,
+                         void* out, int bs_a, int bs_b, int M, int N, int K, int* dev_status, void* stream);
 
 /* FP8 flash-attention forward, head dim 64.  q [B,H,M,64], k [B,H,N,64],
  * vt [B,H,64,ceil16(N)] e4m3 contiguous; out [B,H,M,64] e4m3 (saturating) or

@@ -35,6 +35,8 @@ SIGNATURES = {
     "q8k_tokenwise_quant": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_i64, _c_ptr]),
     "q8k_fast_hadamard_transform": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_i64, _c_int, _c_i64, _c_f32, _c_ptr]),
     "q8k_hadamard_quant": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_i64, _c_f32, _c_ptr]),
+    "q8k_norm_modulate_quant": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_i64, _c_f32,
+                                         _c_ptr]),
     "q8k_rms_norm": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_ptr]),
     "q8k_rope": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_i64, _c_int, _c_i64, _c_ptr]),
     "q8k_fma_8bit": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_i64, _c_i64,
@@ -44,6 +46,8 @@ SIGNATURES = {
                            _c_int, _c_int, _c_ptr, _c_ptr]),
     "q8k_fp8_mm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_ptr, _c_ptr]),
+    "q8k_mm_gate_residual": (_c_int, [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr,
+                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]),
     "q8k_flash_attention": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f32,
                                      _c_ptr, _c_ptr, _c_ptr]),
     "q8k_flash_attention_strided": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,

@@ -106,6 +106,13 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
           "l"(*reinterpret_cast<unsigned long long*>(&c)));
     return *reinterpret_cast<float2*>(&d);
 }
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
 __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
     unsigned long long d;
     asm("add.rn.f32x2 %0, %1, %2;"
@@ -369,8 +376,13 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     __syncwarp();
                     ptx::tmem_ld_32x32b_x16(t_lane + kAttnOCol + h * 16, orow);
                     ptx::tmem_wait_ld();
+                    const float2 al2 = make_float2(alpha, alpha);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) orow[j] = __float_as_uint(__uint_as_float(orow[j]) * alpha);
+                    for (int j = 0; j < 16; j += 2) {
+                        const float2 m = fmul2(make_float2(__uint_as_float(orow[j]), __uint_as_float(orow[j + 1])), al2);
+                        orow[j] = __float_as_uint(m.x);
+                        orow[j + 1] = __float_as_uint(m.y);
+                    }
                     ptx::tmem_st_32x32b_x16(t_lane + kAttnOCol + h * 16, orow);
                 }
                 ptx::tmem_wait_st();

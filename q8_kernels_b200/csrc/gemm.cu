@@ -42,7 +42,7 @@ struct GemmSmem {
     static constexpr int kDynamic = kTotal + 1024;          // slack to align the base to 1024 B
 };
 
-template <bool INT8, int BN, int STAGES, bool GELU, bool OUT_E4M3>
+template <bool INT8, int BN, int STAGES, bool GELU, bool OUT_E4M3, bool RESID>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
@@ -201,6 +201,7 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const bool row_ok = row < p.M;
             const float sa = row_ok ? p.a_scales[(p.batch_a ? (int64_t)batch * p.M : 0) + row] : 0.f;
             const int64_t out_row = ((int64_t)batch * p.M + row) * p.N;
+            const int64_t gate_row = RESID ? (((int64_t)batch * p.M + row) / p.rows_per_gate) * p.N : 0;
             const int col_base = half * HALF_COLS;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + col_base;
 
@@ -246,10 +247,29 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         for (int v4 = 0; v4 < 4; ++v4) {
                             if (v4 * 8 < valid) {
                                 uint32_t w[4];
+                                uint4 rs = make_uint4(0, 0, 0, 0), gt = make_uint4(0, 0, 0, 0);
+                                if constexpr (RESID) {
+                                    rs = *reinterpret_cast<const uint4*>(p.resid + out_row + nc + v4 * 8);
+                                    if (p.gate != nullptr)
+                                        gt = *reinterpret_cast<const uint4*>(p.gate + gate_row + nc + v4 * 8);
+                                }
 #pragma unroll
                                 for (int q = 0; q < 4; ++q) {
                                     const int j = v4 * 8 + q * 2;
                                     __nv_bfloat162 b2 = __floats2bfloat162_rn(y[j], y[j + 1]);
+                                    if constexpr (RESID) {
+                                        // out = bf16(bf16(gate * bf16(y)) + resid): the roundings of the separate
+                                        // torch ops of blocks/ltx_transformer_block.py (gate*x, then + residual)
+                                        float2 f = __bfloat1622float2(b2);
+                                        if (p.gate != nullptr) {
+                                            const uint32_t gw = (&gt.x)[q];
+                                            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw));
+                                            f = __bfloat1622float2(__floats2bfloat162_rn(g.x * f.x, g.y * f.y));
+                                        }
+                                        const uint32_t rw = (&rs.x)[q];
+                                        const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw));
+                                        b2 = __floats2bfloat162_rn(f.x + r2.x, f.y + r2.y);
+                                    }
                                     w[q] = *reinterpret_cast<uint32_t*>(&b2);
                                 }
                                 reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -289,10 +309,10 @@ int gemm_num_sms() {
     return g_num_sms;
 }
 
-template <bool INT8, int BN, int STAGES, bool GELU, bool OUT_E4M3>
+template <bool INT8, int BN, int STAGES, bool GELU, bool OUT_E4M3, bool RESID = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t st) {
     using L = GemmSmem<BN, STAGES>;
-    auto kern = gemm_8bit_kernel<INT8, BN, STAGES, GELU, OUT_E4M3>;
+    auto kern = gemm_8bit_kernel<INT8, BN, STAGES, GELU, OUT_E4M3, RESID>;
     Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
     const int grid = p.total_tiles < gemm_num_sms() ? p.total_tiles : gemm_num_sms();
     kern<<<grid, kGemmThreads, L::kDynamic, st>>>(ta, tb, p);
@@ -302,7 +322,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 
 static int gemm_8bit(bool int8, const void* a, const void* b, const float* bias, const float* a_scales,
                      const float* b_scales, void* out, int out_dtype, int bs_a, int bs_b, int M, int N, int K,
-                     int fuse_gelu, int* dev_status, void* stream) {
+                     int fuse_gelu, int* dev_status, void* stream, const void* resid = nullptr,
+                     const void* gate = nullptr, int64_t rows_per_gate = 1) {
     const char* op = int8 ? "q8_mm" : "fp8_mm";
     Q8K_REQUIRE(a && b && a_scales && b_scales && out, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
     Q8K_REQUIRE(bs_a >= 1 && bs_b >= 1 && (bs_a == bs_b || bs_a == 1 || bs_b == 1), Q8K_ERR_INVALID_ARG,
@@ -341,6 +362,9 @@ static int gemm_8bit(bool int8, const void* a, const void* b, const float* bias,
     p.bias = bias;
     p.out = out;
     p.status = dev_status;
+    p.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
+    p.gate = reinterpret_cast<const __nv_bfloat16*>(gate);
+    p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1;
     p.M = M; p.N = N; p.K = K;
     p.batch_a = bs_a > 1; p.batch_b = bs_b > 1;
     p.m_tiles = (M + kGemmBM - 1) / kGemmBM;
@@ -355,8 +379,13 @@ static int gemm_8bit(bool int8, const void* a, const void* b, const float* bias,
     // Large problems run on 256 x 256 tiles owned by CTA pairs (half the B-operand shared-memory
     // traffic per CTA); small ones, or devices that cannot co-schedule the pairs, on 128 x 256 tiles.
     static const bool pair_disabled = getenv("Q8K_GEMM_NO_PAIR") != nullptr;
+    const bool fuse_resid = resid != nullptr;
+    if (fuse_resid) {
+        Q8K_REQUIRE(!gelu && !e4m3, Q8K_ERR_UNSUPPORTED, "%s: the gate/residual tail needs a bf16 output without GELU", op);
+        Q8K_REQUIRE(aligned16(resid) && aligned16(gate), Q8K_ERR_INVALID_ARG, "%s: gate and residual must be 16-byte aligned", op);
+    }
     if (!pair_disabled && M > kGemmBM && N > 128) {
-        const int rc = launch_gemm_pair(int8, gelu, e4m3, a, b, p, bs_a, bs_b, st);
+        const int rc = launch_gemm_pair(int8, gelu, e4m3, fuse_resid, a, b, p, bs_a, bs_b, st);
         if (rc != Q8K_ERR_UNSUPPORTED) return rc;
     }
 #define Q8K_GEMM_DISPATCH(I8, BNV, ST)                                                        \
@@ -366,6 +395,12 @@ static int gemm_8bit(bool int8, const void* a, const void* b, const float* bias,
         return e4m3 ? launch_gemm<I8, BNV, ST, false, true>(ta, tb, p, st)                    \
                     : launch_gemm<I8, BNV, ST, false, false>(ta, tb, p, st);                  \
     } while (0)
+    if (fuse_resid) {
+        if (int8) return bn256 ? launch_gemm<true, 256, 4, false, false, true>(ta, tb, p, st)
+                               : launch_gemm<true, 128, 6, false, false, true>(ta, tb, p, st);
+        return bn256 ? launch_gemm<false, 256, 4, false, false, true>(ta, tb, p, st)
+                     : launch_gemm<false, 128, 6, false, false, true>(ta, tb, p, st);
+    }
     if (int8) {
         if (bn256) Q8K_GEMM_DISPATCH(true, 256, 4);
         Q8K_GEMM_DISPATCH(true, 128, 6);
@@ -382,6 +417,17 @@ extern "C" int q8k_q8_mm(const void* a, const void* b, const float* bias, const 
                          int K, int fuse_gelu, int* dev_status, void* stream) {
     return q8k::gemm_8bit(true, a, b, bias, a_scales, b_scales, out, out_dtype, bs_a, bs_b, M, N, K, fuse_gelu,
                           dev_status, stream);
+}
+
+extern "C" int q8k_mm_gate_residual(int int8, const void* a, const void* b, const float* bias, const float* a_scales,
+                                    const float* b_scales, const void* gate, const void* resid, int64_t rows_per_gate,
+                                    void* out, int bs_a, int bs_b, int M, int N, int K, int* dev_status, void* stream) {
+    if (resid == nullptr) {
+        q8k::set_error_detail("mm_gate_residual: null residual");
+        return Q8K_ERR_INVALID_ARG;
+    }
+    return q8k::gemm_8bit(int8 != 0, a, b, bias, a_scales, b_scales, out, Q8K_DT_BF16, bs_a, bs_b, M, N, K, 0, dev_status,
+                          stream, resid, gate, rows_per_gate);
 }
 
 extern "C" int q8k_fp8_mm(const void* a, const void* b, const float* bias, const float* a_scales,

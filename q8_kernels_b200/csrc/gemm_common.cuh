@@ -21,6 +21,10 @@ struct GemmParams {
     int M, N, K;
     int batch_a, batch_b;             // 1 when that operand carries a batch dim
     int m_tiles, n_tiles, total_tiles;
+    // optional fused tail (bf16 output only): out = bf16(bf16(gate[row / rows_per_gate, n] * y) + resid[row, n])
+    const __nv_bfloat16* resid;
+    const __nv_bfloat16* gate;        // may be null: plain residual add
+    int64_t rows_per_gate;
 };
 
 __device__ __forceinline__ float gelu_tanh_fast(float y) {
@@ -36,7 +40,7 @@ int gemm_num_sms();
 // CTA-pair (cta_group::2) variant: 256 x 256 output tiles per cluster of two CTAs.  Returns
 // Q8K_ERR_UNSUPPORTED (without touching the error detail) when the device cannot co-schedule
 // the clusters, in which case the caller falls back to the single-CTA kernel.
-int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, const void* a, const void* b, const GemmParams& p,
+int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, bool resid, const void* a, const void* b, const GemmParams& p,
                      int bs_a, int bs_b, cudaStream_t st);
 
 }  // namespace q8k

@@ -45,7 +45,7 @@ struct PairParams {
     int total_tiles2;
 };
 
-template <bool INT8, bool GELU, bool OUT_E4M3>
+template <bool INT8, bool GELU, bool OUT_E4M3, bool RESID>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const PairParams pp) {
@@ -213,6 +213,7 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             const bool row_ok = row < p.M;
             const float sa = row_ok ? p.a_scales[(p.batch_a ? (int64_t)batch * p.M : 0) + row] : 0.f;
             const int64_t out_row = ((int64_t)batch * p.M + row) * p.N;
+            const int64_t gate_row = RESID ? (((int64_t)batch * p.M + row) / p.rows_per_gate) * p.N : 0;
             const int col_base = half * HALF_COLS;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kPairBN + col_base;
 
@@ -257,10 +258,29 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         for (int v4 = 0; v4 < 4; ++v4) {
                             if (v4 * 8 < valid) {
                                 uint32_t w[4];
+                                uint4 rs = make_uint4(0, 0, 0, 0), gt = make_uint4(0, 0, 0, 0);
+                                if constexpr (RESID) {
+                                    rs = *reinterpret_cast<const uint4*>(p.resid + out_row + nc + v4 * 8);
+                                    if (p.gate != nullptr)
+                                        gt = *reinterpret_cast<const uint4*>(p.gate + gate_row + nc + v4 * 8);
+                                }
 #pragma unroll
                                 for (int q = 0; q < 4; ++q) {
                                     const int j = v4 * 8 + q * 2;
                                     __nv_bfloat162 b2 = __floats2bfloat162_rn(y[j], y[j + 1]);
+                                    if constexpr (RESID) {
+                                        // out = bf16(bf16(gate * bf16(y)) + resid): the roundings of the separate
+                                        // torch ops of blocks/ltx_transformer_block.py (gate*x, then + residual)
+                                        float2 f = __bfloat1622float2(b2);
+                                        if (p.gate != nullptr) {
+                                            const uint32_t gw = (&gt.x)[q];
+                                            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw));
+                                            f = __bfloat1622float2(__floats2bfloat162_rn(g.x * f.x, g.y * f.y));
+                                        }
+                                        const uint32_t rw = (&rs.x)[q];
+                                        const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw));
+                                        b2 = __floats2bfloat162_rn(f.x + r2.x, f.y + r2.y);
+                                    }
                                     w[q] = *reinterpret_cast<uint32_t*>(&b2);
                                 }
                                 reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -289,9 +309,9 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 }
 
 // ------------------------------------------------------------------ host side
-template <bool INT8, bool GELU, bool OUT_E4M3>
+template <bool INT8, bool GELU, bool OUT_E4M3, bool RESID = false>
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const PairParams& pp, cudaStream_t st) {
-    auto kern = gemm_8bit_pair_kernel<INT8, GELU, OUT_E4M3>;
+    auto kern = gemm_8bit_pair_kernel<INT8, GELU, OUT_E4M3, RESID>;
     Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamic));
     // how many 2-CTA clusters can be resident at once (cached per kernel variant)
     static int max_clusters = -1;
@@ -316,7 +336,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const PairP
     return Q8K_OK;
 }
 
-int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, const void* a, const void* b, const GemmParams& p,
+int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, bool resid, const void* a, const void* b, const GemmParams& p,
                      int bs_a, int bs_b, cudaStream_t st) {
     const char* op = int8 ? "q8_mm" : "fp8_mm";
     CUtensorMap ta, tb;
@@ -347,6 +367,10 @@ int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, const void* a, const v
         return out_e4m3 ? launch_pair<I8, false, true>(ta, tb, pp, st)                \
                         : launch_pair<I8, false, false>(ta, tb, pp, st);              \
     } while (0)
+    if (resid) {
+        return int8 ? launch_pair<true, false, false, true>(ta, tb, pp, st)
+                    : launch_pair<false, false, false, true>(ta, tb, pp, st);
+    }
     if (int8) Q8K_PAIR(true);
     Q8K_PAIR(false);
 #undef Q8K_PAIR

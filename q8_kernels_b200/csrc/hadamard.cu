@@ -278,10 +278,15 @@ __device__ __forceinline__ uint8_t quantize_fast(float y) {
     else return float_to_e4m3_c10(y);
 }
 
-template <typename Tin, typename Tout, int LOG_N, int LOG_V, int ROWS, Epilogue EPI>
+// NORM_MOD adds the block's pre-linear prologue in front of the transform, with the bf16 roundings
+// of the separate ops it replaces: n = bf16(x * rsqrt(mean x^2)); u = bf16(bf16(n * bf16(1 + s)) + h)
+// where s, h are the per-batch modulation rows (bf16 [rows / rows_per_mod, dim]).
+template <typename Tin, typename Tout, int LOG_N, int LOG_V, int ROWS, Epilogue EPI, bool NORM_MOD = false>
 __global__ void __launch_bounds__(ROWS << (LOG_N - LOG_V))
 hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __restrict__ scales,
-                    int64_t rows, int dim, int64_t x_row_stride, float scale) {
+                    int64_t rows, int dim, int64_t x_row_stride, float scale,
+                    const __nv_bfloat16* __restrict__ mod_scale = nullptr,
+                    const __nv_bfloat16* __restrict__ mod_shift = nullptr, int64_t rows_per_mod = 1) {
     constexpr int N = 1 << LOG_N;
     constexpr int V = 1 << LOG_V;
     constexpr int T = N / V;                                   // threads per row
@@ -329,6 +334,42 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
             u.raw = stage[item ^ (t & (ITEMS - 1))];
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[k * 8 + j] = to_float<Tin>(u.e[j]);
+        }
+    }
+    if constexpr (NORM_MOD) {
+        static_assert(std::is_same_v<Tin, __nv_bfloat16>, "the norm + modulation prologue takes bf16 rows");
+        __shared__ float red_ss[32];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) ss = fmaf(v[i], v[i], ss);
+#pragma unroll
+        for (int m = 1; m < (T < 32 ? T : 32); m <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        if constexpr (T > 32) {
+            constexpr int WPR = T / 32;
+            if ((threadIdx.x & 31) == 0) red_ss[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            ss = red_ss[r_in_cta * WPR];
+#pragma unroll
+            for (int k = 1; k < WPR; ++k) ss += red_ss[r_in_cta * WPR + k];
+        }
+        const float rr = rsqrtf(ss * (1.0f / (float)dim));
+        const int64_t mrow = row_ok ? row / rows_per_mod : 0;
+        const __nv_bfloat16* sc = mod_scale + mrow * dim + t * V;
+        const __nv_bfloat16* sh = mod_shift + mrow * dim + t * V;
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+            if (t * V + k * 8 < dim) {
+                float s8[8], h8[8];
+                load_vec<__nv_bfloat16, 8>(sc + k * 8, s8);
+                load_vec<__nv_bfloat16, 8>(sh + k * 8, h8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float n = round_through<__nv_bfloat16>(__fmul_rn(v[k * 8 + j], rr));
+                    const float m1 = round_through<__nv_bfloat16>(__fadd_rn(1.0f, s8[j]));
+                    const float tm = round_through<__nv_bfloat16>(__fmul_rn(n, m1));
+                    v[k * 8 + j] = round_through<__nv_bfloat16>(__fadd_rn(tm, h8[j]));
+                }
+            }
         }
     }
     butterfly_consecutive<V>(v);
@@ -443,7 +484,7 @@ static int launch_hadamard(const void* x, void* out, float* scales, int64_t rows
         constexpr int smem = NR * (1 << LN) * (int)sizeof(float);                                         \
         if (smem > 48 * 1024)                                                                             \
             Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));   \
-        kern<<<(unsigned)((rows + NR - 1) / NR), NR << (LN - LV), smem, st>>>(xi, o, scales, rows, dim, stride, scale); \
+        kern<<<(unsigned)((rows + NR - 1) / NR), NR << (LN - LV), smem, st>>>(xi, o, scales, rows, dim, stride, scale, nullptr, nullptr, 1); \
     } break
         // (row length, values per thread, rows per CTA), chosen by measurement: the plain transform
         // likes more values per thread (fewer exchanges), the fused quantizer more threads
@@ -458,6 +499,33 @@ static int launch_hadamard(const void* x, void* out, float* scales, int64_t rows
         }
 #undef Q8K_HR
     }
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+// fused RMSNorm + modulation + Hadamard + quantizer (bf16 rows of 512 .. 8192 elements)
+template <typename Tout>
+static int launch_norm_mod_quant(const void* x, const void* mod_scale, const void* mod_shift, void* q, float* scales,
+                                 int64_t rows, int dim, int64_t rows_per_mod, float scale, cudaStream_t st) {
+    int log_n = 9;
+    while ((1 << log_n) < dim) ++log_n;
+    const __nv_bfloat16* xi = (const __nv_bfloat16*)x;
+    const __nv_bfloat16* ms = (const __nv_bfloat16*)mod_scale;
+    const __nv_bfloat16* mh = (const __nv_bfloat16*)mod_shift;
+    Tout* o = (Tout*)q;
+#define Q8K_NM(LN, LV, NR)                                                                                \
+    case LN: {                                                                                            \
+        auto kern = hadamard_row_kernel<__nv_bfloat16, Tout, LN, LV, NR, Epilogue::Quant, true>;          \
+        constexpr int smem = NR * (1 << LN) * (int)sizeof(float);                                         \
+        if (smem > 48 * 1024)                                                                             \
+            Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));   \
+        kern<<<(unsigned)((rows + NR - 1) / NR), NR << (LN - LV), smem, st>>>(xi, o, scales, rows, dim, dim, scale, ms, mh, rows_per_mod); \
+    } break
+    switch (log_n) {
+        Q8K_NM(9, 5, 8); Q8K_NM(10, 5, 4); Q8K_NM(11, 5, 2); Q8K_NM(12, 6, 2); Q8K_NM(13, 6, 1);
+        default: set_error_detail("norm_modulate_quant: dim %d not in [512, 8192]", dim); return Q8K_ERR_UNSUPPORTED;
+    }
+#undef Q8K_NM
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }
@@ -510,6 +578,23 @@ extern "C" int q8k_hadamard_quant(const void* x, int x_dtype, void* q, int q_dty
     if (x_dtype == Q8K_DT_BF16 && q_dtype == Q8K_DT_E4M3) return launch_hadamard<__nv_bfloat16, e4m3_t, Q>(x, q, scales, rows, dim, x_row_stride, scale, st, op);
     if (x_dtype == Q8K_DT_E4M3 && q_dtype == Q8K_DT_I8)   return launch_hadamard<e4m3_t, int8_t, Q>(x, q, scales, rows, dim, x_row_stride, scale, st, op);
     if (x_dtype == Q8K_DT_E4M3 && q_dtype == Q8K_DT_E4M3) return launch_hadamard<e4m3_t, e4m3_t, Q>(x, q, scales, rows, dim, x_row_stride, scale, st, op);
+    set_error_detail("%s: quantised dtype %d is not int8 or e4m3", op, q_dtype);
+    return Q8K_ERR_UNSUPPORTED;
+}
+
+extern "C" int q8k_norm_modulate_quant(const void* x, const void* mod_scale, const void* mod_shift, void* q, int q_dtype,
+                                       float* scales, int64_t rows, int dim, int64_t rows_per_mod, float scale,
+                                       void* stream) {
+    const char* op = "norm_modulate_quant";
+    if (int rc = check_hadamard_args(op, x, Q8K_DT_BF16, q, rows, dim, dim)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(dim >= 257 && dim % 16 == 0, Q8K_ERR_UNSUPPORTED, "%s: dim %d must be a multiple of 16 above 256", op, dim);
+    Q8K_REQUIRE(mod_scale && mod_shift && scales, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE(aligned16(mod_scale) && aligned16(mod_shift), Q8K_ERR_INVALID_ARG, "%s: modulation rows must be 16-byte aligned", op);
+    Q8K_REQUIRE(rows_per_mod >= 1, Q8K_ERR_INVALID_ARG, "%s: rows_per_mod must be >= 1", op);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (q_dtype == Q8K_DT_I8) return launch_norm_mod_quant<int8_t>(x, mod_scale, mod_shift, q, scales, rows, dim, rows_per_mod, scale, st);
+    if (q_dtype == Q8K_DT_E4M3) return launch_norm_mod_quant<e4m3_t>(x, mod_scale, mod_shift, q, scales, rows, dim, rows_per_mod, scale, st);
     set_error_detail("%s: quantised dtype %d is not int8 or e4m3", op, q_dtype);
     return Q8K_ERR_UNSUPPORTED;
 }

@@ -55,7 +55,12 @@ class Attention(nn.Module):
 
     def forward(self, hidden_states, freqs_cis=None, encoder_hidden_states=None, attention_mask=None,
                 non_mm_precision=torch.bfloat16, mm_out_dtype=None, apply_qk_hadamard=True, attn_type="torch",
-                head_shard: Optional[Tuple[int, int]] = None, gather_heads=None):
+                head_shard: Optional[Tuple[int, int]] = None, gather_heads=None,
+                hidden_states_q=None, out_gate=None, out_residual=None):
+        """Reference signature plus: ``head_shard`` / ``gather_heads`` (attention core on a slice of the
+        heads), ``hidden_states_q = (int8, scales)`` when the caller already holds the Hadamard-rotated,
+        quantised ``hidden_states`` (the fused norm + modulation producer), and ``out_gate`` /
+        ``out_residual`` to fold ``gate * out + residual`` into the output projection's epilogue."""
         if attention_mask is not None and attention_mask.ndim > 1 and attn_type == "q8_kernels":
             attention_mask = attention_mask.argmin(-1).squeeze().int()
             if attention_mask.ndim == 0:
@@ -65,7 +70,7 @@ class Attention(nn.Module):
         # Hadamard + quantizer on every call); here each distinct input is quantised once and the
         # int8 rows + scales are shared, which is bit-identical.
         kv_src = encoder_hidden_states if encoder_hidden_states is not None else hidden_states
-        hq, hs = self._quantize_once(hidden_states)
+        hq, hs = hidden_states_q if hidden_states_q is not None else self._quantize_once(hidden_states)
         if encoder_hidden_states is not None:
             kq, ks = self._quantize_once(kv_src)
         else:
@@ -117,5 +122,13 @@ class Attention(nn.Module):
                 raise ValueError("head_shard needs a gather_heads callable that reassembles the channel dim")
             hidden_states = gather_heads(hidden_states)
 
+        if out_residual is not None and mm_out_dtype == torch.bfloat16 and non_mm_precision == torch.bfloat16:
+            oq, os_ = self._quantize_once(hidden_states)
+            return native.mm_gate_residual(oq, self.to_out.weight.data,
+                                           self.to_out.bias.data if self.to_out.bias is not None else None,
+                                           os_, self.to_out.scales, out_gate, out_residual)
         hidden_states = self.to_out(hidden_states, out_dtype=mm_out_dtype)
-        return hidden_states.to(non_mm_precision)
+        hidden_states = hidden_states.to(non_mm_precision)
+        if out_residual is not None:
+            hidden_states = (out_gate * hidden_states if out_gate is not None else hidden_states) + out_residual
+        return hidden_states

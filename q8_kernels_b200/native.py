@@ -8,6 +8,7 @@ synchronises.
 """
 from __future__ import annotations
 
+import math
 from typing import List, Optional, Tuple
 
 import torch
@@ -92,6 +93,31 @@ def hadamard_quant(x: torch.Tensor, scale: float, out_type: Optional[torch.dtype
         check(lib.q8k_hadamard_quant(ptr(x2), dt(x2.dtype), ptr(q), dt(out_type), ptr(scales), rows, dim,
                                      _row_stride(x2), float(scale), stream_ptr(dev)), "hadamard_quant")
     return [q.reshape(shape), scales.reshape(shape[:-1])]
+
+
+def norm_modulate_quant(x: torch.Tensor, mod_scale: torch.Tensor, mod_shift: torch.Tensor,
+                        out_type: Optional[torch.dtype] = None) -> List[torch.Tensor]:
+    """RMS norm (no affine weight) -> ``n * (1 + mod_scale) + mod_shift`` -> Hadamard (1/sqrt(dim)) ->
+    per-token quantizer in one kernel, keeping the bf16 roundings of the separate ops
+    (q8_kernels/blocks/ltx_transformer_block.py:38-39,53-54 + functional/linear.py:30-31).
+    x bf16 [B, S, dim]; mod_scale / mod_shift bf16 [B, 1, dim].  Returns ``[q, scales]``."""
+    dev = require_cuda(x, mod_scale, mod_shift)
+    out_type = torch.int8 if out_type is None else out_type
+    if x.dtype != torch.bfloat16 or mod_scale.dtype != torch.bfloat16 or mod_shift.dtype != torch.bfloat16:
+        raise Q8KernelError("norm_modulate_quant: x and the modulation rows must be bfloat16")
+    if x.dim() != 3 or tuple(mod_scale.shape) != (x.shape[0], 1, x.shape[2]) or mod_shift.shape != mod_scale.shape:
+        raise Q8KernelError("norm_modulate_quant: x must be [B,S,dim] and the modulation rows [B,1,dim]")
+    B, S, dim = x.shape
+    x = x.contiguous()
+    mod_scale = mod_scale.contiguous()
+    mod_shift = mod_shift.contiguous()
+    q = torch.empty((B, S, dim), dtype=out_type, device=dev)
+    scales = torch.empty((B, S), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_norm_modulate_quant(ptr(x), ptr(mod_scale), ptr(mod_shift), ptr(q), dt(out_type), ptr(scales),
+                                          B * S, dim, S, float(1.0 / math.sqrt(dim)), stream_ptr(dev)),
+              "norm_modulate_quant")
+    return [q, scales]
 
 
 def rms_norm(x: torch.Tensor, weights: Optional[torch.Tensor] = None,
@@ -234,6 +260,37 @@ def fp8_mm(a, b, a_scales, b_scales, fuse_gelu: bool, out_type: Optional[torch.d
 def fp8_mm_bias(a, b, bias, a_scales, b_scales, fuse_gelu: bool, out_type: Optional[torch.dtype] = None):
     """csrc/gemm/q8_gemm_api.cpp:227-291."""
     return _gemm(lib.q8k_fp8_mm, "fp8_mm_bias", a, b, bias, a_scales, b_scales, fuse_gelu, out_type, E4M3)
+
+
+def mm_gate_residual(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], a_scales: torch.Tensor,
+                     b_scales: torch.Tensor, gate: Optional[torch.Tensor], resid: torch.Tensor) -> torch.Tensor:
+    """``bf16(bf16(gate * bf16(linear)) + resid)`` with the gate/residual in the GEMM epilogue: the
+    q8_mm_bias (or fp8_mm_bias) call plus the two torch ops of
+    q8_kernels/blocks/ltx_transformer_block.py:41,52,56, bit-identical to running them separately.
+    a int8|e4m3 [B,S,K] (or [M,K]); b [N,K]; gate bf16 [B,1,N] or None; resid bf16 shaped like the output."""
+    dev = require_cuda(a, b, bias, a_scales, b_scales, gate, resid)
+    if a.dtype != b.dtype or a.dtype not in (torch.int8, E4M3):
+        raise Q8KernelError("mm_gate_residual: a and b must both be int8 or both float8_e4m3fn")
+    bs_a, m = (a.shape[0], a.shape[1]) if a.dim() == 3 else (1, a.shape[0])
+    n, k = b.shape
+    if b.dim() != 2 or a.shape[-1] != k:
+        raise Q8KernelError("mm_gate_residual: b must be [N,K] with K matching a")
+    if resid.dtype != torch.bfloat16 or resid.numel() != bs_a * m * n:
+        raise Q8KernelError("mm_gate_residual: resid must be bfloat16 with the output's shape")
+    rows_per_gate = 1
+    if gate is not None:
+        if gate.dtype != torch.bfloat16 or gate.numel() != bs_a * n:
+            raise Q8KernelError("mm_gate_residual: gate must be bfloat16 [B,1,N]")
+        gate = gate.contiguous()
+        rows_per_gate = m
+    a, b, resid = a.contiguous(), b.contiguous(), resid.contiguous()
+    a_scales, b_scales = a_scales.contiguous(), b_scales.contiguous()
+    out = torch.empty((bs_a, m, n), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_mm_gate_residual(int(a.dtype == torch.int8), ptr(a), ptr(b), ptr(bias), ptr(a_scales), ptr(b_scales),
+                                       ptr(gate), ptr(resid), rows_per_gate, ptr(out), bs_a, 1, m, n, k,
+                                       ptr(_lib.status_word(dev)), stream_ptr(dev)), "mm_gate_residual")
+    return out
 
 
 # ---------------------------------------------------------------- flash_attention._C

@@ -162,3 +162,71 @@ def test_ltx_stack_small_against_oracle(q8, cuda_device):
         h = OB.ltx_block(bsd, h, (cos, sin), None, proj, lens, timestep, num_heads=4, head_dim=64)
     err = Hp.rel_fro(got.float(), h.float())
     assert got.shape == (1, S, 256) and err < 2e-2, f"rel fro {err:.3e}"
+
+
+def test_norm_modulate_quant_matches_unfused_chain(q8, cuda_device):
+    """Fused RMSNorm + modulation + Hadamard + quantizer vs the oracle's op-by-op chain.  Only the
+    fp32 summation order of the mean square differs, so all but a few int8 codes are identical."""
+    import math
+    g = Hp.gen(41)
+    B, S, C = 2, 96, 2048
+    x = Hp.activations(B * S, C, seed=42).reshape(B, S, C)
+    sc = (torch.randn(B, 1, C, generator=g) * 0.1).to(torch.bfloat16)
+    sh = (torch.randn(B, 1, C, generator=g) * 0.1).to(torch.bfloat16)
+    n = O.rms_norm(x, None, torch.bfloat16)[0]
+    u = n * (1 + sc) + sh                                      # torch bf16 ops, as the reference block does
+    q_ref, s_ref = O.tokenwise_quant(O.hadamard_transform(u))
+    d = cuda_device
+    q, s = q8.native.norm_modulate_quant(x.to(d), sc.to(d), sh.to(d))
+    assert q.shape == (B, S, C) and s.shape == (B, S)
+    diff = (q.cpu().int() - q_ref.int()).abs()
+    assert diff.max().item() <= 1 and (diff != 0).float().mean().item() < 0.01
+    assert torch.allclose(s.cpu(), s_ref, rtol=1e-2)
+    # against the same chain on the device the agreement is the same
+    nd = q8.native.rms_norm(x.to(d), None, torch.bfloat16)[0]
+    ud = nd * (1 + sc.to(d)) + sh.to(d)
+    qd, sd = q8.native.hadamard_quant(ud, 1 / math.sqrt(C), torch.int8)
+    assert ((q.int() - qd.int()).abs() != 0).float().mean().item() < 0.01
+
+
+@pytest.mark.parametrize("kind", ["int8", "fp8"])
+@pytest.mark.parametrize("with_gate", [True, False])
+@pytest.mark.parametrize("M,N,K", [(200, 512, 256), (384, 2048, 2048), (96, 128, 128)])
+def test_mm_gate_residual_is_bit_identical_to_separate_ops(q8, cuda_device, kind, with_gate, M, N, K):
+    qd = torch.int8 if kind == "int8" else E4M3
+    d = cuda_device
+    B = 2
+    a = Hp.activations(B * M, K, seed=M + N)
+    w = Hp.weights(N, K, seed=K)
+    aq, sa = O.tokenwise_quant(a, qd)
+    wq, sw = O.tokenwise_quant(w, qd)
+    aq, sa = aq.reshape(B, M, K).to(d), sa.reshape(B, M).to(d)
+    wq, sw = wq.to(d), sw.to(d)
+    bias = Hp.bias_vec(N, seed=1).to(d)
+    g = Hp.gen(2)
+    gate = torch.randn(B, 1, N, generator=g).to(torch.bfloat16).to(d) if with_gate else None
+    resid = torch.randn(B, M, N, generator=g).to(torch.bfloat16).to(d)
+    mm = q8.native.q8_mm_bias if kind == "int8" else q8.native.fp8_mm_bias
+    y = mm(aq, wq, bias, sa, sw, False, torch.bfloat16)
+    want = (gate * y if with_gate else y) + resid
+    got = q8.native.mm_gate_residual(aq, wq, bias, sa, sw, gate, resid)
+    assert got.shape == (B, M, N)
+    assert torch.equal(got, want)
+
+
+def test_block_fused_path_equals_op_by_op_path(q8, cuda_device):
+    blk, _ = _random_block(q8, 512, 8, 64, 512, cuda_device, seed=51)
+    blk.scale_shift_table.data = blk.scale_shift_table.data.to(torch.bfloat16)
+    g = Hp.gen(52)
+    S, T = 4 * 6 * 8, 40
+    d = cuda_device
+    x = torch.randn(2, S, 512, generator=g).to(torch.bfloat16).to(d)
+    text = torch.randn(2, T, 512, generator=g).to(torch.bfloat16).to(d)
+    ts = (torch.randn(2, 1, 6 * 512, generator=g) * 0.1).to(torch.bfloat16).to(d)
+    grid = torch.stack(torch.meshgrid(torch.arange(4), torch.arange(6), torch.arange(8), indexing="ij"), 0)
+    cos, sin = O.precompute_freqs_cis(grid.reshape(1, 3, -1).float(), dim=512)
+    lens = torch.tensor([11, 40], dtype=torch.int32, device=d)
+    a = blk(x, (cos.to(d), sin.to(d)), None, text, lens, ts, attn_type="q8_kernels", fuse=True)
+    b = blk(x, (cos.to(d), sin.to(d)), None, text, lens, ts, attn_type="q8_kernels", fuse=False)
+    err = Hp.rel_fro(a.float(), b.float())
+    assert err < 4e-3, f"rel fro {err:.3e}"                   # only 1/rms summation order differs, amplified by int8 codes
