@@ -174,6 +174,19 @@ Q8K_API int q8k_attention_prep(const void* q, const void* k, const void* v,
                        int64_t v_stride_b, int64_t v_stride_s, int64_t v_stride_h,
                        int apply_hadamard, float qk_scale, void* stream);
 
+/* Q or K after its projection, in one pass per tensor: RMS norm over all H*64 channels with the fp32
+ * weight norm_w (result rounded to bf16), optional rotary embedding with fp32 tables [S, H*64] shared
+ * by the batch (rounded to bf16; pass NULL tables to skip), per-head 64-point Hadamard times qk_scale
+ * when apply_hadamard, c10 e4m3 cast, output head-major [B,H,S,64].  x bf16 rows of H*64 channels with
+ * row stride x_row_stride.  Replaces q_norm/k_norm + apply_rope of q8_kernels/modules/attention.py:54-68
+ * and the Q/K half of the glue in functional/flash_attention.py:50-54; q8k_attention_prep_v is the V
+ * half (transpose, zero pad, cast) of q8k_attention_prep on its own.                                  */
+Q8K_API int q8k_qk_norm_rope_prep(const void* x, int64_t x_row_stride, const float* norm_w, const float* cos_t,
+                          const float* sin_t, void* out8, int B, int S, int H, int apply_hadamard,
+                          float qk_scale, void* stream);
+Q8K_API int q8k_attention_prep_v(const void* v, void* vt8, int B, int H, int S_kv, int64_t v_stride_b,
+                         int64_t v_stride_s, int64_t v_stride_h, void* stream);
+
 /* Whole activation side of Q8Linear / FP8Linear in one call: fused Hadamard +
  * per-token quantizer into caller-provided scratch, then the GEMM.
  * x bf16 [M,K]; w int8|e4m3 [N,K] with w_scales [N]; workspace must hold

@@ -582,6 +582,87 @@ attn_prep_qk_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ o
     }
 }
 
+// Q / K after their projection, fused: RMS norm over all H*64 channels with an fp32 weight (bf16
+// result), optional rotary embedding with shared fp32 tables [S, H*64] (bf16 result), then per head
+// the 64-point Hadamard times `scale` and the c10 e4m3 cast, written head-major [B,H,S,64].  One
+// CTA per token row, 8 elements per thread (thread t owns channels 8t..8t+7, head t/8).  The
+// roundings are those of the separate kernels (rms_norm_kernel, rope_kernel, attn_prep_qk_kernel);
+// only the summation order of the mean square differs from rms_norm_kernel.
+__global__ void __launch_bounds__(1024)
+attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
+                              const float* __restrict__ norm_w, const float* __restrict__ cos_t,
+                              const float* __restrict__ sin_t, uint8_t* __restrict__ out, int H, int S,
+                              int apply_hadamard, float scale) {
+    __shared__ float red[32];
+    const int t = threadIdx.x;
+    const int lane = t & 31;
+    const int dim = H * 64;
+    const int64_t row = blockIdx.x;                            // b * S + s
+    const int s_idx = (int)(row % S);
+    const int64_t b = row / S;
+    float v[8];
+    load_vec<__nv_bfloat16, 8>(x + row * x_row_stride + t * 8, v);
+
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[t >> 5] = ss;
+    __syncthreads();
+    float tot = red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+    const float r = rsqrtf(tot * (1.0f / (float)dim));
+
+    float wv[8];
+    load_vec<float, 8>(norm_w + t * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        v[j] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v[j], r), wv[j])));
+
+    if (cos_t != nullptr) {
+        float c[8], sn[8], o[8];
+        load_vec<float, 8>(cos_t + (int64_t)s_idx * dim + t * 8, c);
+        load_vec<float, 8>(sin_t + (int64_t)s_idx * dim + t * 8, sn);
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            o[j]     = __fadd_rn(__fmul_rn(-v[j + 1], sn[j]), __fmul_rn(v[j], c[j]));
+            o[j + 1] = __fadd_rn(__fmul_rn(v[j], sn[j + 1]), __fmul_rn(v[j + 1], c[j + 1]));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(o[j]));
+    }
+
+    if (apply_hadamard) {
+#pragma unroll
+        for (int st = 1; st < 8; st <<= 1) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int lo = j & (st - 1);
+                const int i = ((j - lo) << 1) + lo;
+                const float a = v[i], bb = v[i + st];
+                v[i] = __fadd_rn(a, bb);
+                v[i + st] = __fsub_rn(a, bb);
+            }
+        }
+#pragma unroll
+        for (int mk = 1; mk < 8; mk <<= 1) {
+            const float sign = (lane & mk) ? -1.f : 1.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[j], mk);
+                v[j] = __fmaf_rn(sign, v[j], other);           // other - v for the upper lane, v + other for the lower: exact
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(v[j], scale);
+    }
+    union { uint2 v2; uint8_t bts[8]; } o8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o8.bts[j] = float_to_e4m3_c10(v[j]);
+    const int h = t >> 3, sub = t & 7;
+    *reinterpret_cast<uint2*>(out + ((b * H + h) * S + s_idx) * 64 + sub * 8) = o8.v2;
+}
+
 // V: [B,S,H,64] bf16 view -> vt [B,H,64,S_pad] e4m3, zero padded along S.
 __global__ void __launch_bounds__(256)
 attn_prep_v_kernel(const __nv_bfloat16* __restrict__ v, uint8_t* __restrict__ vt, int H, int S, int S_pad,
@@ -717,6 +798,40 @@ extern "C" int q8k_attention_prep(const void* q, const void* k, const void* v, v
         attn_prep_v_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)v, (uint8_t*)vt8, H, S_kv, s_pad,
                                                  v_stride_b, v_stride_s, v_stride_h);
     }
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_qk_norm_rope_prep(const void* x, int64_t x_row_stride, const float* norm_w, const float* cos_t,
+                                     const float* sin_t, void* out8, int B, int S, int H, int apply_hadamard,
+                                     float qk_scale, void* stream) {
+    const char* op = "qk_norm_rope_prep";
+    Q8K_REQUIRE(x && norm_w && out8, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), Q8K_ERR_INVALID_ARG, "%s: give both rotary tables or neither", op);
+    Q8K_REQUIRE(B > 0 && S > 0 && H > 0 && H <= 128, Q8K_ERR_INVALID_ARG, "%s: bad shape B=%d S=%d H=%d (H <= 128)", op, B, S, H);
+    Q8K_REQUIRE(H % 4 == 0, Q8K_ERR_UNSUPPORTED, "%s: H must be a multiple of 4", op);
+    Q8K_REQUIRE(x_row_stride >= (int64_t)H * 64 && x_row_stride % 8 == 0, Q8K_ERR_INVALID_ARG,
+                "%s: row stride must be >= H*64 and a multiple of 8 elements", op);
+    Q8K_REQUIRE(aligned16(x) && aligned16(norm_w) && aligned16(cos_t) && aligned16(sin_t) && aligned16(out8),
+                Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
+    Q8K_REQUIRE((int64_t)B * S <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
+    attn_qk_norm_rope_prep_kernel<<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, x_row_stride, norm_w, cos_t, sin_t, (uint8_t*)out8, H, S, apply_hadamard, qk_scale);
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_attention_prep_v(const void* v, void* vt8, int B, int H, int S_kv, int64_t v_stride_b,
+                                    int64_t v_stride_s, int64_t v_stride_h, void* stream) {
+    const char* op = "attention_prep_v";
+    Q8K_REQUIRE(v && vt8, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE(B > 0 && H > 0 && S_kv > 0 && (int64_t)B * H <= 65535, Q8K_ERR_INVALID_ARG, "%s: bad shape", op);
+    Q8K_REQUIRE(v_stride_b % 8 == 0 && v_stride_s % 8 == 0 && v_stride_h % 8 == 0 && aligned16(v) && aligned16(vt8),
+                Q8K_ERR_INVALID_ARG, "%s: strides must be multiples of 8 elements and pointers 16-byte aligned", op);
+    const int s_pad = (S_kv + 15) / 16 * 16;
+    dim3 grid((unsigned)((S_kv + 63) / 64), (unsigned)(B * H));
+    attn_prep_v_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)v, (uint8_t*)vt8, H, S_kv, s_pad,
+                                                              v_stride_b, v_stride_s, v_stride_h);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }

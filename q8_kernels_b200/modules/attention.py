@@ -76,18 +76,33 @@ class Attention(nn.Module):
         else:
             kq, ks = hq, hs
         query = self.to_q(hq, hs, out_dtype=mm_out_dtype)
+        key = self.to_k(kq, ks, out_dtype=mm_out_dtype)
+        value = self.to_v(kq, ks, out_dtype=mm_out_dtype)
+        batch_size = query.shape[0]
+        heads = self.num_heads
+        rope_here = encoder_hidden_states is None and self.use_rope
+
+        # Fast path: q/k norm + RoPE + per-head Hadamard + e4m3 cast as one kernel per tensor, straight
+        # into the attention kernel's operand layout (same roundings as the op-by-op path below).
+        if (attn_type == "q8_kernels" and self.qk_rms_norm and self.head_dim == 64 and head_shard is None
+                and apply_qk_hadamard and query.dtype == torch.bfloat16 and non_mm_precision == torch.bfloat16
+                and query.dim() == 3 and (not rope_here or freqs_cis[0].shape[0] == 1)):
+            scale = math.sqrt(1 / 64) * math.sqrt(64 ** -0.5)
+            fc = freqs_cis if rope_here else None
+            q8_ = native.qk_norm_rope_prep(query, self.q_norm.weight, fc, heads, True, scale)
+            k8_ = native.qk_norm_rope_prep(key, self.k_norm.weight, fc, heads, True, scale)
+            vt8 = native.attention_prep_v(value.view(batch_size, -1, heads, self.head_dim).transpose(1, 2))
+            hidden_states = native.flash_attention(q8_, k8_, vt8, 1.0, attention_mask, None, token_major_out=True)
+            hidden_states = hidden_states.transpose(1, 2).reshape(batch_size, -1, heads * self.head_dim)
+            return self._project_out(hidden_states, non_mm_precision, mm_out_dtype, out_gate, out_residual)
+
         if self.qk_rms_norm:
             query = self.q_norm(query, non_mm_precision)
-        key = self.to_k(kq, ks, out_dtype=mm_out_dtype)
-        if self.qk_rms_norm:
             key = self.k_norm(key, non_mm_precision)
-        value = self.to_v(kq, ks, out_dtype=mm_out_dtype)
-        if encoder_hidden_states is None and self.use_rope:
+        if rope_here:
             query = Q8F.rope.apply_rope(query, freqs_cis[0], freqs_cis[1], out_type=non_mm_precision)
             key = Q8F.rope.apply_rope(key, freqs_cis[0], freqs_cis[1], out_type=non_mm_precision)
 
-        batch_size = query.shape[0]
-        heads = self.num_heads
         query = query.view(batch_size, -1, heads, self.head_dim).transpose(1, 2)
         key = key.view(batch_size, -1, heads, self.head_dim).transpose(1, 2)
         value = value.view(batch_size, -1, heads, self.head_dim).transpose(1, 2)
@@ -122,6 +137,9 @@ class Attention(nn.Module):
                 raise ValueError("head_shard needs a gather_heads callable that reassembles the channel dim")
             hidden_states = gather_heads(hidden_states)
 
+        return self._project_out(hidden_states, non_mm_precision, mm_out_dtype, out_gate, out_residual)
+
+    def _project_out(self, hidden_states, non_mm_precision, mm_out_dtype, out_gate, out_residual):
         if out_residual is not None and mm_out_dtype == torch.bfloat16 and non_mm_precision == torch.bfloat16:
             oq, os_ = self._quantize_once(hidden_states)
             return native.mm_gate_residual(oq, self.to_out.weight.data,

@@ -371,6 +371,50 @@ def attention_prep(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, apply_hada
     return q8, k8, vt8
 
 
+def qk_norm_rope_prep(x: torch.Tensor, norm_w: torch.Tensor, freqs_cis, num_heads: int, apply_hadamard: bool,
+                      qk_scale: float) -> torch.Tensor:
+    """q_norm / k_norm (RMS norm with fp32 weight over all heads) + optional RoPE + per-head Hadamard +
+    e4m3 cast in one kernel: x bf16 [B,S,H*64] (row-strided views allowed) -> e4m3 [B,H,S,64], with the
+    bf16 roundings of q8_kernels/modules/attention.py:54-68 and functional/flash_attention.py:50-54.
+    ``freqs_cis`` is None or (cos, sin) fp32 [1,S,H*64]."""
+    dev = require_cuda(x, norm_w)
+    if x.dtype != torch.bfloat16 or x.dim() != 3 or x.shape[2] != num_heads * 64 or x.stride(2) != 1:
+        raise Q8KernelError("qk_norm_rope_prep: x must be bfloat16 [B,S,H*64] with contiguous channels")
+    if norm_w.dtype != torch.float32 or norm_w.numel() != x.shape[2]:
+        raise Q8KernelError("qk_norm_rope_prep: norm weight must be float32 [H*64]")
+    B, S, C = x.shape
+    if x.stride(0) != S * x.stride(1) or x.stride(1) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    cos = sin = None
+    if freqs_cis is not None:
+        cos, sin = freqs_cis
+        if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.numel() != S * C or sin.numel() != S * C:
+            raise Q8KernelError("qk_norm_rope_prep: rotary tables must be float32 [1,S,H*64]")
+        cos, sin = cos.contiguous(), sin.contiguous()
+    out = torch.empty((B, num_heads, S, 64), dtype=E4M3, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_qk_norm_rope_prep(ptr(x), x.stride(1), ptr(norm_w.contiguous()), ptr(cos), ptr(sin), ptr(out), B, S,
+                                        num_heads, int(bool(apply_hadamard)), float(qk_scale), stream_ptr(dev)),
+              "qk_norm_rope_prep")
+    return out
+
+
+def attention_prep_v(v: torch.Tensor) -> torch.Tensor:
+    """V half of attention_prep: bf16 [B,H,S,64] view -> e4m3 [B,H,64,ceil16(S)] (transposed, zero padded)."""
+    dev = require_cuda(v)
+    B, H, S, D = v.shape
+    if D != 64 or v.dtype != torch.bfloat16:
+        raise Q8KernelError("attention_prep_v: v must be bfloat16 with head dim 64")
+    if v.stride(3) != 1 or any(s % 8 for s in v.stride()[:3]) or v.data_ptr() % 16:
+        v = v.contiguous()
+    s_pad = (S + 15) // 16 * 16
+    vt8 = torch.empty((B, H, 64, s_pad), dtype=E4M3, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_attention_prep_v(ptr(v), ptr(vt8), B, H, S, v.stride(0), v.stride(2), v.stride(1), stream_ptr(dev)),
+              "attention_prep_v")
+    return vt8
+
+
 # ---------------------------------------------------------------- fused linear chain
 
 _workspaces = {}

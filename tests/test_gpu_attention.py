@@ -131,3 +131,45 @@ def test_token_major_output_is_the_same_values(nat, cuda_device):
     assert torch.equal(a, b)
     flat = b.transpose(1, 2).reshape(2, 200, 4 * 64)
     assert flat.data_ptr() == b.data_ptr()                     # the module's reshape is a view, not a copy
+
+
+@pytest.mark.parametrize("B,S,H,rope", [(2, 96, 32, True), (1, 130, 32, False), (1, 64, 4, True), (1, 33, 128, True)])
+def test_fused_qk_norm_rope_prep_matches_the_op_chain(nat, cuda_device, B, S, H, rope):
+    """One kernel for q_norm/k_norm + RoPE + head Hadamard + e4m3 cast against the same steps as
+    separate kernels (rms_norm -> rope -> attention_prep) and against the oracle's chain.  The only
+    difference allowed is the summation order of the mean square: an occasional last-bit flip."""
+    C = H * 64
+    x = Hp.activations(B * S, C, seed=S + H).view(B, S, C).to(cuda_device)
+    w = (1.0 + 0.1 * torch.randn(C, generator=Hp.gen(5))).to(cuda_device)
+    ang = torch.rand(1, S, C, generator=Hp.gen(6)) * 6.28
+    cos, sin = ang.cos().to(cuda_device), ang.sin().to(cuda_device)
+    scale = math.sqrt(1 / 64) * math.sqrt(64 ** -0.5)
+    fc = (cos, sin) if rope else None
+    got = nat.qk_norm_rope_prep(x, w, fc, H, True, scale)
+    assert got.shape == (B, H, S, 64) and got.dtype == E4M3
+
+    y = nat.rms_norm(x, w, torch.bfloat16)[0]
+    if rope:
+        y = nat.rope(y, cos, sin, torch.bfloat16)
+    yh = y.view(B, S, H, 64).transpose(1, 2)
+    want, _, _ = nat.attention_prep(yh, yh, yh, True, scale)
+    mism = (Hp.bits(got) != Hp.bits(want)).float().mean().item()
+    assert mism < 2e-3, f"{mism:.2e} of the bytes differ from the op chain"
+    assert Hp.rel_fro(got.float(), want.float()) < 2e-3
+
+    yo = O.rms_norm(x.cpu(), w.cpu(), torch.bfloat16)[0]
+    if rope:
+        yo = O.rope(yo, cos.cpu(), sin.cpu(), torch.bfloat16)
+    ref = O.hadamard_transform(yo.view(B, S, H, 64).transpose(1, 2), scale=scale, out_dtype=E4M3)
+    assert Hp.rel_fro(got.float().cpu(), ref.float()) < 2e-3
+
+    # a row-strided view (e.g. a slice of a wider projection output) gives the same bytes
+    wide = torch.zeros(B, S, C + 64, dtype=torch.bfloat16, device=cuda_device)
+    wide[..., :C] = x
+    assert torch.equal(Hp.bits(nat.qk_norm_rope_prep(wide[..., :C], w, fc, H, True, scale)), Hp.bits(got))
+
+
+def test_attention_prep_v_alone_matches_attention_prep(nat, cuda_device):
+    q, k, v = (t.to(cuda_device) for t in Hp.qkv(2, 3, 77, 64, seed=9))
+    _, _, want = nat.attention_prep(q, k, v, False, 1.0)
+    assert torch.equal(Hp.bits(nat.attention_prep_v(v)), Hp.bits(want))

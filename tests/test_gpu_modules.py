@@ -230,3 +230,37 @@ def test_block_fused_path_equals_op_by_op_path(q8, cuda_device):
     b = blk(x, (cos.to(d), sin.to(d)), None, text, lens, ts, attn_type="q8_kernels", fuse=False)
     err = Hp.rel_fro(a.float(), b.float())
     assert err < 4e-3, f"rel fro {err:.3e}"                   # only 1/rms summation order differs, amplified by int8 codes
+
+
+def test_block_is_cuda_graph_capturable(q8, cuda_device):
+    """No op of the block synchronises or allocates outside torch's allocator, so a whole block
+    forward can be captured once and replayed (the reference does this per module with its graph.py)."""
+    blk, _ = _random_block(q8, 512, 8, 64, 512, cuda_device, seed=61)
+    blk.scale_shift_table.data = blk.scale_shift_table.data.to(torch.bfloat16)
+    g = Hp.gen(62)
+    d = cuda_device
+    S, T = 4 * 4 * 8, 24
+    x = torch.randn(1, S, 512, generator=g).to(torch.bfloat16).to(d)
+    text = torch.randn(1, T, 512, generator=g).to(torch.bfloat16).to(d)
+    ts = (torch.randn(1, 1, 6 * 512, generator=g) * 0.1).to(torch.bfloat16).to(d)
+    grid = torch.stack(torch.meshgrid(torch.arange(4), torch.arange(4), torch.arange(8), indexing="ij"), 0)
+    cos, sin = O.precompute_freqs_cis(grid.reshape(1, 3, -1).float(), dim=512)
+    freqs = (cos.to(d), sin.to(d))
+    lens = torch.tensor([17], dtype=torch.int32, device=d)
+    with torch.no_grad():
+        side = torch.cuda.Stream(device=d)
+        side.wait_stream(torch.cuda.current_stream(d))
+        with torch.cuda.stream(side):
+            for _ in range(2):                                  # warm-up: first-call set-up happens outside the capture
+                eager = blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels")
+        torch.cuda.current_stream(d).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels")
+        x2 = torch.randn(1, S, 512, generator=g).to(torch.bfloat16).to(d)
+        want = blk(x2, freqs, None, text, lens, ts, attn_type="q8_kernels").clone()
+        x.copy_(x2)
+        graph.replay()
+        torch.cuda.synchronize(d)
+    assert torch.equal(captured, want)
+    assert not torch.equal(captured, eager)
