@@ -219,11 +219,11 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const uint32_t(&rc)[32] = r[c & 1];
                     float y[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float accf = INT8 ? (float)(int)rc[j] : __uint_as_float(rc[j]);
-                        float v = fmaf(accf, sa * col_scale_smem[cl + j], bias_smem[cl + j]);
-                        if constexpr (GELU) v = gelu_tanh_fast(v);
-                        y[j] = v;
+                    for (int j = 0; j < 32; j += 2) {
+                        const float2 v = epilogue_pair<INT8, GELU>(rc[j], rc[j + 1], make_float2(sa, sa),
+                                                                   col_scale_smem + cl + j, bias_smem + cl + j);
+                        y[j] = v.x;
+                        y[j + 1] = v.y;
                     }
                     const int valid = min(32, p.N - nc);       // N % 16 == 0, so valid is 16 or 32
                     if constexpr (OUT_E4M3) {

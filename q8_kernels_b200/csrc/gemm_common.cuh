@@ -35,6 +35,31 @@ __device__ __forceinline__ float gelu_tanh_fast(float y) {
     return 0.5f * y * (1.0f + t);
 }
 
+// Same function on a pair of adjacent columns with packed fp32 instructions (6 issue slots + 2
+// tanh for two outputs): 0.5 y (1 + tanh(y (k0 + k0 k1 y^2))).
+__device__ __forceinline__ float2 gelu_tanh_fast2(float2 y) {
+    const float2 p = ffma2(fmul2(y, y), make_float2(0.7978845608028654f * 0.044715f, 0.7978845608028654f * 0.044715f),
+                           make_float2(0.7978845608028654f, 0.7978845608028654f));
+    const float2 u = fmul2(p, y);
+    float2 t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t.x) : "f"(u.x));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t.y) : "f"(u.y));
+    const float2 h = fmul2(y, make_float2(0.5f, 0.5f));
+    return ffma2(h, t, h);
+}
+
+// Epilogue arithmetic of one row on two adjacent columns: acc * (sa * sb[n]) + bias[n], then the
+// optional GELU.  r0, r1 are the raw 32-bit accumulator words (int32 or fp32); sb / bias point
+// at the pair's column in shared memory (8-byte aligned).
+template <bool INT8, bool GELU>
+__device__ __forceinline__ float2 epilogue_pair(uint32_t r0, uint32_t r1, float2 sa2, const float* sb, const float* bias) {
+    const float2 acc = INT8 ? make_float2((float)(int)r0, (float)(int)r1)
+                            : make_float2(__uint_as_float(r0), __uint_as_float(r1));
+    float2 y = ffma2(acc, fmul2(sa2, *reinterpret_cast<const float2*>(sb)), *reinterpret_cast<const float2*>(bias));
+    if constexpr (GELU) y = gelu_tanh_fast2(y);
+    return y;
+}
+
 int gemm_num_sms();
 
 // CTA-pair (cta_group::2) variant: 256 x 256 output tiles per cluster of two CTAs.  Returns

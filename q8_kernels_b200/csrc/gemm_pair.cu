@@ -13,7 +13,13 @@
 //   warp 1     TMEM allocation (both CTAs); in the leader (even rank) one thread issues the MMAs
 //              and commits to the "empty" / "accumulator full" barriers of both CTAs
 //   warps 2-9  epilogue of the CTA's own 128 rows x 256 columns (identical arithmetic to the
-//              single-CTA kernel); "accumulator free" arrivals of both CTAs go to the leader
+//              single-CTA kernel); "accumulator free" arrivals of both CTAs go to the leader.
+//              Output leaves through shared memory: each warp writes its 32 x 32 chunk into a
+//              swizzled staging box and one lane hands it to a TMA store, so global memory sees
+//              whole 32/64-byte row segments instead of 32 row-strided 16-byte stores per
+//              instruction (which held the epilogue, and with it the K = 2048 shapes, back).
+//              The fused gate/residual variant and outputs whose row pitch is not a multiple of
+//              16 bytes keep the direct stores.
 // No multicast loads are used: every CTA fetches its own operand tiles with plain TMA loads.
 
 #include "gemm_common.cuh"
@@ -28,14 +34,22 @@ struct PairSmem {
     static constexpr int kABytes = kGemmBM * kGemmBK;              // 16 KB: this CTA's 128 rows of A
     static constexpr int kBBytes = (kPairBN / 2) * kGemmBK;        // 16 KB: this CTA's 128 rows of B
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kBarOffset = kPairStages * kStageBytes;
+    // output staging: per epilogue warp two 32-row boxes of 64 bytes per row (bf16) or 32 (e4m3)
+    static constexpr int kStoreBoxBytes = 32 * 64;
+    static constexpr int kStoreOffset = kPairStages * kStageBytes;
+    static constexpr int kStoreBytes = (kGemmEpilogueThreads / 32) * 2 * kStoreBoxBytes;
+    static constexpr int kBarOffset = kStoreOffset + kStoreBytes;
     static constexpr int kNumBars = 2 * kPairStages + 4;
     static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
     static constexpr int kAbortOffset = kTmemPtrOffset + 4;
-    static constexpr int kColScaleOffset = (kAbortOffset + 4 + 15) & ~15;
+    static constexpr int kPriorOffset = kAbortOffset + 4;
+    static constexpr int kColScaleOffset = (kPriorOffset + 4 + 15) & ~15;
     static constexpr int kBiasOffset = kColScaleOffset + kPairBN * 4;
     static constexpr int kTotal = kBiasOffset + kPairBN * 4;
-    static constexpr int kDynamic = kTotal + 1024;
+    // No alignment slack: the kernel has no static shared memory, so the dynamic window starts on
+    // a 1024-byte boundary; the kernel checks that and reports instead of running misaligned.
+    static constexpr int kDynamic = kTotal;
+    static_assert(kDynamic <= 227 * 1024, "pair GEMM shared memory");
 };
 
 struct PairParams {
@@ -43,20 +57,23 @@ struct PairParams {
     int m_tiles2;                            // 256-row tiles per batch entry
     int n_tiles2;
     int total_tiles2;
+    int tma_store;                           // 1: the epilogue stores through tmap_c
 };
 
 template <bool INT8, bool GELU, bool OUT_E4M3, bool RESID>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const PairParams pp) {
+                      const __grid_constant__ CUtensorMap tmap_c, const PairParams pp) {
     using L = PairSmem;
     const GemmParams& p = pp.g;
     constexpr uint32_t IDESC = INT8 ? ptx::make_idesc_s8(2 * kGemmBM, kPairBN) : ptx::make_idesc_e4m3(2 * kGemmBM, kPairBN);
 
-    extern __shared__ uint8_t smem_raw[];
-    // the dynamic shared window starts at the same offset in both CTAs, so rounding up keeps the two layouts congruent
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t smem_base = ptx::smem_u32(smem);
+    if (smem_base & 1023u) {                                   // same offset in both CTAs: both leave
+        if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (11 << 8));
+        return;
+    }
     const uint32_t bar_base = smem_base + L::kBarOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
@@ -77,15 +94,15 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
     // A launch that follows a failed one on the same status word does nothing.  The leader reads
     // the word and hands its decision to the peer, so the two CTAs of a pair always agree.
-    __shared__ int prior_failure;
+    volatile int* prior_failure = reinterpret_cast<volatile int*>(smem + L::kPriorOffset);
     if (threadIdx.x == 0 && leader) {
         const int v = p.status != nullptr ? *reinterpret_cast<volatile int*>(p.status) : 0;
-        prior_failure = v;
-        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(ptx::mapa_shared(ptx::smem_u32(&prior_failure), 1)), "r"(v)
+        *prior_failure = v;
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(ptx::mapa_shared(smem_base + L::kPriorOffset, 1)), "r"(v)
                      : "memory");
     }
     ptx::cluster_sync_all();
-    const bool skip = prior_failure != 0;
+    const bool skip = *prior_failure != 0;
     if (skip) return;
 
     if (threadIdx.x == 0) {
@@ -102,6 +119,7 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         ptx::fence_proxy_async_smem();
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        if (pp.tma_store) ptx::prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair<kPairTmemCols>(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)));
@@ -185,7 +203,10 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int epi_tid = threadIdx.x - 64;
         constexpr int HALF_COLS = kPairBN / 2;
         constexpr int NCH = HALF_COLS / 32;
+        const bool staged = !RESID && pp.tma_store != 0;
+        const uint32_t store_base = smem_base + L::kStoreOffset + (uint32_t)(warp - 2) * 2u * L::kStoreBoxBytes;
         uint32_t tile_i = 0;
+        uint32_t store_i = 0;                                  // stores issued by this warp: picks the staging box
         bool ok = true;
         for (int tile = cluster_id; tile < pp.total_tiles2; tile += num_clusters, ++tile_i) {
             const int n_blk = tile % pp.n_tiles2;
@@ -226,15 +247,57 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 if (c + 1 < NCH) ptx::tmem_ld_32x32b_x32(t_row + (c + 1) * 32, r[(c + 1) & 1]);
                 const int cl = col_base + c * 32;
                 const int nc = n0 + cl;
-                if (row_ok && nc < p.N) {
+                if (staged) {
+                    if (nc < p.N) {                            // warp-uniform
+                        const uint32_t(&rc)[32] = r[c & 1];
+                        constexpr int ROW_BYTES = OUT_E4M3 ? 32 : 64;
+                        const uint32_t box = store_base + (store_i & 1u) * L::kStoreBoxBytes;
+                        ++store_i;
+                        // the store that last used this box (two stores ago) must have read it out
+                        if (lane == 0) ptx::bulk_wait_group_read<1>();
+                        __syncwarp();
+                        uint32_t w[ROW_BYTES / 4];
+#pragma unroll
+                        for (int j = 0; j < 32; j += (OUT_E4M3 ? 4 : 2)) {
+                            const float2 y0 = epilogue_pair<INT8, GELU>(rc[j], rc[j + 1], make_float2(sa, sa),
+                                                                        col_scale_smem + cl + j, bias_smem + cl + j);
+                            if constexpr (OUT_E4M3) {
+                                const float2 y1 = epilogue_pair<INT8, GELU>(rc[j + 2], rc[j + 3], make_float2(sa, sa),
+                                                                            col_scale_smem + cl + j + 2, bias_smem + cl + j + 2);
+                                w[j / 4] = (uint32_t)float2_to_e4m3x2_sat(y0.x, y0.y) |
+                                           ((uint32_t)float2_to_e4m3x2_sat(y1.x, y1.y) << 16);
+                            } else {
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(y0.x, y0.y);
+                                w[j / 2] = *reinterpret_cast<uint32_t*>(&b2);
+                            }
+                        }
+                        // row `lane` of the box, 16-byte pieces XOR-swizzled as the tensor map expects
+                        // (SWIZZLE_64B: piece ^= (row >> 1) & 3; SWIZZLE_32B: piece ^= (row >> 2) & 1)
+                        const uint32_t row_addr = box + (uint32_t)lane * ROW_BYTES;
+                        const uint32_t sw = OUT_E4M3 ? ((uint32_t)lane >> 2) & 1u : ((uint32_t)lane >> 1) & 3u;
+#pragma unroll
+                        for (int q = 0; q < ROW_BYTES / 16; ++q) {
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)q ^ sw) << 4)),
+                                         "r"(w[4 * q]), "r"(w[4 * q + 1]), "r"(w[4 * q + 2]), "r"(w[4 * q + 3])
+                                         : "memory");
+                        }
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_3d(&tmap_c, box, nc * (OUT_E4M3 ? 1 : 2),
+                                              m_blk * 2 * kGemmBM + (int)rank * kGemmBM + quarter * 32, batch);
+                            ptx::bulk_commit_group();
+                        }
+                    }
+                } else if (row_ok && nc < p.N) {
                     const uint32_t(&rc)[32] = r[c & 1];
                     float y[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float accf = INT8 ? (float)(int)rc[j] : __uint_as_float(rc[j]);
-                        float v = fmaf(accf, sa * col_scale_smem[cl + j], bias_smem[cl + j]);
-                        if constexpr (GELU) v = gelu_tanh_fast(v);
-                        y[j] = v;
+                    for (int j = 0; j < 32; j += 2) {
+                        const float2 v = epilogue_pair<INT8, GELU>(rc[j], rc[j + 1], make_float2(sa, sa),
+                                                                   col_scale_smem + cl + j, bias_smem + cl + j);
+                        y[j] = v.x;
+                        y[j + 1] = v.y;
                     }
                     const int valid = min(32, p.N - nc);
                     if constexpr (OUT_E4M3) {
@@ -294,6 +357,7 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(leader_tmem_empty_bar(acc));   // the leader's MMA thread waits for both CTAs
         }
+        if (staged && lane == 0) ptx::bulk_wait_group<0>();     // this warp's stores are performed before the CTA may exit
         if (!ok && p.status != nullptr && epi_tid == 0) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (10 << 8));
     }
 
@@ -310,7 +374,8 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
 // ------------------------------------------------------------------ host side
 template <bool INT8, bool GELU, bool OUT_E4M3, bool RESID = false>
-static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const PairParams& pp, cudaStream_t st) {
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const PairParams& pp,
+                       cudaStream_t st) {
     auto kern = gemm_8bit_pair_kernel<INT8, GELU, OUT_E4M3, RESID>;
     Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamic));
     // how many 2-CTA clusters can be resident at once (cached per kernel variant)
@@ -331,7 +396,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const PairP
     }
     if (max_clusters < 8) return Q8K_ERR_UNSUPPORTED;
     const int clusters = pp.total_tiles2 < max_clusters ? pp.total_tiles2 : max_clusters;
-    kern<<<2 * clusters, kGemmThreads, PairSmem::kDynamic, st>>>(ta, tb, pp);
+    kern<<<2 * clusters, kGemmThreads, PairSmem::kDynamic, st>>>(ta, tb, tc, pp);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }
@@ -355,6 +420,17 @@ int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, bool resid, const void
     PairParams pp;
     pp.g = p;
     const int batch = bs_a > bs_b ? bs_a : bs_b;
+    // output map for the staged epilogue: [batch, M, N] as bytes, 32-column boxes of 32 rows
+    CUtensorMap tc = ta;
+    const uint64_t esz = out_e4m3 ? 1 : 2;
+    pp.tma_store = 0;
+    if (!resid && ((uint64_t)p.N * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+        const uint64_t dims[3] = {(uint64_t)p.N * esz, (uint64_t)p.M, (uint64_t)batch};
+        const uint64_t strides[2] = {(uint64_t)p.N * esz, (uint64_t)p.M * (uint64_t)p.N * esz};
+        const uint32_t box[3] = {(uint32_t)(32 * esz), 32u, 1u};
+        if (int rc = make_byte_tensor_map(&tc, p.out, 3, dims, strides, box, (int)(32 * esz), op)) return rc;
+        pp.tma_store = 1;
+    }
     pp.m_tiles2 = (p.M + 2 * kGemmBM - 1) / (2 * kGemmBM);
     pp.n_tiles2 = (p.N + kPairBN - 1) / kPairBN;
     const int64_t total = (int64_t)pp.m_tiles2 * pp.n_tiles2 * batch;
@@ -362,14 +438,14 @@ int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, bool resid, const void
     pp.total_tiles2 = (int)total;
 #define Q8K_PAIR(I8)                                                                  \
     do {                                                                              \
-        if (gelu) return out_e4m3 ? launch_pair<I8, true, true>(ta, tb, pp, st)       \
-                                  : launch_pair<I8, true, false>(ta, tb, pp, st);     \
-        return out_e4m3 ? launch_pair<I8, false, true>(ta, tb, pp, st)                \
-                        : launch_pair<I8, false, false>(ta, tb, pp, st);              \
+        if (gelu) return out_e4m3 ? launch_pair<I8, true, true>(ta, tb, tc, pp, st)       \
+                                  : launch_pair<I8, true, false>(ta, tb, tc, pp, st);     \
+        return out_e4m3 ? launch_pair<I8, false, true>(ta, tb, tc, pp, st)                \
+                        : launch_pair<I8, false, false>(ta, tb, tc, pp, st);              \
     } while (0)
     if (resid) {
-        return int8 ? launch_pair<true, false, false, true>(ta, tb, pp, st)
-                    : launch_pair<false, false, false, true>(ta, tb, pp, st);
+        return int8 ? launch_pair<true, false, false, true>(ta, tb, tc, pp, st)
+                    : launch_pair<false, false, false, true>(ta, tb, tc, pp, st);
     }
     if (int8) Q8K_PAIR(true);
     Q8K_PAIR(false);

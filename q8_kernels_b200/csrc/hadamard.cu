@@ -139,27 +139,6 @@ hadamard_small_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* 
 // Butterflies work on packed fp32 pairs (add/sub.f32x2), so a stage costs half an instruction per
 // element; only the stride-1 stage is scalar.
 
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
-    unsigned long long d;
-    asm("add.rn.f32x2 %0, %1, %2;"
-        : "=l"(d)
-        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
-    return *reinterpret_cast<float2*>(&d);
-}
-__device__ __forceinline__ float2 fsub2(float2 a, float2 b) {
-    unsigned long long d;
-    asm("sub.rn.f32x2 %0, %1, %2;"
-        : "=l"(d)
-        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
-    return *reinterpret_cast<float2*>(&d);
-}
-__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
-    unsigned long long d;
-    asm("mul.rn.f32x2 %0, %1, %2;"
-        : "=l"(d)
-        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
-    return *reinterpret_cast<float2*>(&d);
-}
 
 __device__ __forceinline__ int swz4(int q) { return q ^ ((q >> 3) & 7); }      // float4-chunk swizzle
 
