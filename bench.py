@@ -471,7 +471,7 @@ def main():
                          "peak_basis": f"2 x {peaks['_source']} sustained dense bf16 cuBLAS rate "
                                        f"({peaks['bf16_tflops_sustained']} TFLOP/s); FP8 issues at twice the bf16 rate",
                          "frac_of_nominal_4500": round(per_gpu / 4500.0, 4),
-                         "kernel": "gemm_8bit_kernel<fp8,BN=256,4 stages>",
+                         "kernel": "gemm_8bit_pair_kernel<fp8> (cta_group::2, 256x256 tiles, 6 stages, TMA-store epilogue)",
                          "flops_per_launch_avg": flops / len(sweep_cases()),
                          "avg_launch_ms": round(ms_step / len(sweep_cases()), 5)},
         }

@@ -184,6 +184,11 @@ Q8K_API int q8k_attention_prep(const void* q, const void* k, const void* v,
 Q8K_API int q8k_qk_norm_rope_prep(const void* x, int64_t x_row_stride, const float* norm_w, const float* cos_t,
                           const float* sin_t, void* out8, int B, int S, int H, int apply_hadamard,
                           float qk_scale, void* stream);
+/* The same for Q and K of one self-attention in a single launch (both [B*S, H*64] with the same row
+ * stride, e.g. two column slices of one fused projection output): the rotary table rows are read once. */
+Q8K_API int q8k_qk_norm_rope_prep_pair(const void* xq, const void* xk, int64_t x_row_stride, const float* norm_wq,
+                               const float* norm_wk, const float* cos_t, const float* sin_t, void* outq8,
+                               void* outk8, int B, int S, int H, int apply_hadamard, float qk_scale, void* stream);
 Q8K_API int q8k_attention_prep_v(const void* v, void* vt8, int B, int H, int S_kv, int64_t v_stride_b,
                          int64_t v_stride_s, int64_t v_stride_h, void* stream);
 

@@ -55,6 +55,8 @@ SIGNATURES = {
     "q8k_attention_prep": (_c_int, [_c_ptr] * 6 + [_c_int] * 4 + [_c_i64] * 9 + [_c_int, _c_f32, _c_ptr]),
     "q8k_qk_norm_rope_prep": (_c_int, [_c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                        _c_f32, _c_ptr]),
+    "q8k_qk_norm_rope_prep_pair": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
+                                            _c_int, _c_int, _c_int, _c_f32, _c_ptr]),
     "q8k_attention_prep_v": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_ptr]),
     "q8k_linear_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "q8k_linear": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,

@@ -566,16 +566,24 @@ attn_prep_qk_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ o
 // CTA per token row, 8 elements per thread (thread t owns channels 8t..8t+7, head t/8).  The
 // roundings are those of the separate kernels (rms_norm_kernel, rope_kernel, attn_prep_qk_kernel);
 // only the summation order of the mean square differs from rms_norm_kernel.
+// With a second tensor (x2 / norm_w2 / out2 non-null: K next to Q, same shape and row stride) the
+// grid is twice as long and neighbouring CTAs handle Q and K of the same token, so the rotary
+// table row is fetched from DRAM once.
 __global__ void __launch_bounds__(1024)
-attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
-                              const float* __restrict__ norm_w, const float* __restrict__ cos_t,
-                              const float* __restrict__ sin_t, uint8_t* __restrict__ out, int H, int S,
-                              int apply_hadamard, float scale) {
+attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x2,
+                              int64_t x_row_stride, const float* __restrict__ norm_w,
+                              const float* __restrict__ norm_w2, const float* __restrict__ cos_t,
+                              const float* __restrict__ sin_t, uint8_t* __restrict__ out,
+                              uint8_t* __restrict__ out2, int H, int S, int apply_hadamard, float scale) {
     __shared__ float red[32];
     const int t = threadIdx.x;
     const int lane = t & 31;
     const int dim = H * 64;
-    const int64_t row = blockIdx.x;                            // b * S + s
+    int64_t row = blockIdx.x;                                  // b * S + s
+    if (x2 != nullptr) {
+        if (blockIdx.x & 1) { x = x2; norm_w = norm_w2; out = out2; }
+        row = blockIdx.x >> 1;
+    }
     const int s_idx = (int)(row % S);
     const int64_t b = row / S;
     float v[8];
@@ -794,7 +802,30 @@ extern "C" int q8k_qk_norm_rope_prep(const void* x, int64_t x_row_stride, const 
                 Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
     Q8K_REQUIRE((int64_t)B * S <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
     attn_qk_norm_rope_prep_kernel<<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)x, x_row_stride, norm_w, cos_t, sin_t, (uint8_t*)out8, H, S, apply_hadamard, qk_scale);
+        (const __nv_bfloat16*)x, nullptr, x_row_stride, norm_w, nullptr, cos_t, sin_t, (uint8_t*)out8, nullptr, H, S,
+        apply_hadamard, qk_scale);
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_qk_norm_rope_prep_pair(const void* xq, const void* xk, int64_t x_row_stride, const float* norm_wq,
+                                          const float* norm_wk, const float* cos_t, const float* sin_t, void* outq8,
+                                          void* outk8, int B, int S, int H, int apply_hadamard, float qk_scale,
+                                          void* stream) {
+    const char* op = "qk_norm_rope_prep_pair";
+    Q8K_REQUIRE(xq && xk && norm_wq && norm_wk && outq8 && outk8, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), Q8K_ERR_INVALID_ARG, "%s: give both rotary tables or neither", op);
+    Q8K_REQUIRE(B > 0 && S > 0 && H > 0 && H <= 128, Q8K_ERR_INVALID_ARG, "%s: bad shape B=%d S=%d H=%d (H <= 128)", op, B, S, H);
+    Q8K_REQUIRE(H % 4 == 0, Q8K_ERR_UNSUPPORTED, "%s: H must be a multiple of 4", op);
+    Q8K_REQUIRE(x_row_stride >= (int64_t)H * 64 && x_row_stride % 8 == 0, Q8K_ERR_INVALID_ARG,
+                "%s: row stride must be >= H*64 and a multiple of 8 elements", op);
+    Q8K_REQUIRE(aligned16(xq) && aligned16(xk) && aligned16(norm_wq) && aligned16(norm_wk) && aligned16(cos_t) &&
+                    aligned16(sin_t) && aligned16(outq8) && aligned16(outk8),
+                Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
+    Q8K_REQUIRE((int64_t)B * S * 2 <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
+    attn_qk_norm_rope_prep_kernel<<<(unsigned)((int64_t)B * S * 2), H * 8, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)xq, (const __nv_bfloat16*)xk, x_row_stride, norm_wq, norm_wk, cos_t, sin_t, (uint8_t*)outq8,
+        (uint8_t*)outk8, H, S, apply_hadamard, qk_scale);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }

@@ -18,8 +18,7 @@
 //              swizzled staging box and one lane hands it to a TMA store, so global memory sees
 //              whole 32/64-byte row segments instead of 32 row-strided 16-byte stores per
 //              instruction (which held the epilogue, and with it the K = 2048 shapes, back).
-//              The fused gate/residual variant and outputs whose row pitch is not a multiple of
-//              16 bytes keep the direct stores.
+//              Outputs whose row pitch is not a multiple of 16 bytes keep the direct stores.
 // No multicast loads are used: every CTA fetches its own operand tiles with plain TMA loads.
 
 #include "gemm_common.cuh"
@@ -203,7 +202,7 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int epi_tid = threadIdx.x - 64;
         constexpr int HALF_COLS = kPairBN / 2;
         constexpr int NCH = HALF_COLS / 32;
-        const bool staged = !RESID && pp.tma_store != 0;
+        const bool staged = pp.tma_store != 0;
         const uint32_t store_base = smem_base + L::kStoreOffset + (uint32_t)(warp - 2) * 2u * L::kStoreBoxBytes;
         uint32_t tile_i = 0;
         uint32_t store_i = 0;                                  // stores issued by this warp: picks the staging box
@@ -256,29 +255,57 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         // the store that last used this box (two stores ago) must have read it out
                         if (lane == 0) ptx::bulk_wait_group_read<1>();
                         __syncwarp();
-                        uint32_t w[ROW_BYTES / 4];
-#pragma unroll
-                        for (int j = 0; j < 32; j += (OUT_E4M3 ? 4 : 2)) {
-                            const float2 y0 = epilogue_pair<INT8, GELU>(rc[j], rc[j + 1], make_float2(sa, sa),
-                                                                        col_scale_smem + cl + j, bias_smem + cl + j);
-                            if constexpr (OUT_E4M3) {
-                                const float2 y1 = epilogue_pair<INT8, GELU>(rc[j + 2], rc[j + 3], make_float2(sa, sa),
-                                                                            col_scale_smem + cl + j + 2, bias_smem + cl + j + 2);
-                                w[j / 4] = (uint32_t)float2_to_e4m3x2_sat(y0.x, y0.y) |
-                                           ((uint32_t)float2_to_e4m3x2_sat(y1.x, y1.y) << 16);
-                            } else {
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(y0.x, y0.y);
-                                w[j / 2] = *reinterpret_cast<uint32_t*>(&b2);
-                            }
-                        }
                         // row `lane` of the box, 16-byte pieces XOR-swizzled as the tensor map expects
                         // (SWIZZLE_64B: piece ^= (row >> 1) & 3; SWIZZLE_32B: piece ^= (row >> 2) & 1)
                         const uint32_t row_addr = box + (uint32_t)lane * ROW_BYTES;
                         const uint32_t sw = OUT_E4M3 ? ((uint32_t)lane >> 2) & 1u : ((uint32_t)lane >> 1) & 3u;
+                        const float2 sa2 = make_float2(sa, sa);
 #pragma unroll
                         for (int q = 0; q < ROW_BYTES / 16; ++q) {
+                            uint32_t w[4];
+                            if constexpr (OUT_E4M3) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int j = q * 16 + e * 4;
+                                    const float2 y0 = epilogue_pair<INT8, GELU>(rc[j], rc[j + 1], sa2, col_scale_smem + cl + j,
+                                                                                bias_smem + cl + j);
+                                    const float2 y1 = epilogue_pair<INT8, GELU>(rc[j + 2], rc[j + 3], sa2,
+                                                                                col_scale_smem + cl + j + 2, bias_smem + cl + j + 2);
+                                    w[e] = (uint32_t)float2_to_e4m3x2_sat(y0.x, y0.y) |
+                                           ((uint32_t)float2_to_e4m3x2_sat(y1.x, y1.y) << 16);
+                                }
+                            } else {
+                                uint4 rs = make_uint4(0, 0, 0, 0), gt = make_uint4(0, 0, 0, 0);
+                                if constexpr (RESID) {
+                                    if (row_ok && nc + q * 8 < p.N) {
+                                        rs = *reinterpret_cast<const uint4*>(p.resid + out_row + nc + q * 8);
+                                        if (p.gate != nullptr)
+                                            gt = *reinterpret_cast<const uint4*>(p.gate + gate_row + nc + q * 8);
+                                    }
+                                }
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int j = q * 8 + e * 2;
+                                    const float2 y0 = epilogue_pair<INT8, GELU>(rc[j], rc[j + 1], sa2, col_scale_smem + cl + j,
+                                                                                bias_smem + cl + j);
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(y0.x, y0.y);
+                                    if constexpr (RESID) {
+                                        // out = bf16(bf16(gate * bf16(y)) + resid), the roundings of the separate torch ops
+                                        float2 f = __bfloat1622float2(b2);
+                                        if (p.gate != nullptr) {
+                                            const uint32_t gw = (&gt.x)[e];
+                                            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw));
+                                            f = __bfloat1622float2(__floats2bfloat162_rn(g.x * f.x, g.y * f.y));
+                                        }
+                                        const uint32_t rw = (&rs.x)[e];
+                                        const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw));
+                                        b2 = __floats2bfloat162_rn(f.x + r2.x, f.y + r2.y);
+                                    }
+                                    w[e] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
+                            }
                             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)q ^ sw) << 4)),
-                                         "r"(w[4 * q]), "r"(w[4 * q + 1]), "r"(w[4 * q + 2]), "r"(w[4 * q + 3])
+                                         "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
                                          : "memory");
                         }
                         ptx::fence_proxy_async_smem();
@@ -424,7 +451,7 @@ int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, bool resid, const void
     CUtensorMap tc = ta;
     const uint64_t esz = out_e4m3 ? 1 : 2;
     pp.tma_store = 0;
-    if (!resid && ((uint64_t)p.N * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+    if (((uint64_t)p.N * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
         const uint64_t dims[3] = {(uint64_t)p.N * esz, (uint64_t)p.M, (uint64_t)batch};
         const uint64_t strides[2] = {(uint64_t)p.N * esz, (uint64_t)p.M * (uint64_t)p.N * esz};
         const uint32_t box[3] = {(uint32_t)(32 * esz), 32u, 1u};

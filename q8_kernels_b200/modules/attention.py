@@ -42,6 +42,30 @@ class Attention(nn.Module):
         self.to_v = Q8Linear(kv_dim, self.inner_dim, bias=bias)
         self.to_out = Q8Linear(self.inner_dim, out_dim, out_bias)
 
+    def _stacked(self, key, layers):
+        """Weights, biases and scales of projections that share an input, stacked along the output
+        dim; rebuilt whenever one of the layers' tensors is replaced or modified in place."""
+        cache = self.__dict__.setdefault("_stacked_cache", {})
+        tag = tuple((l.weight.data_ptr(), l.weight._version, l.scales.data_ptr(), l.scales._version,
+                     None if l.bias is None else (l.bias.data_ptr(), l.bias._version)) for l in layers)
+        hit = cache.get(key)
+        if hit is None or hit[0] != tag:
+            w = torch.cat([l.weight.data for l in layers], dim=0)
+            sc = torch.cat([l.scales for l in layers], dim=0)
+            b = None
+            if any(l.bias is not None for l in layers):
+                b = torch.cat([l.bias.data if l.bias is not None else
+                               torch.zeros(l.out_features, dtype=torch.float32, device=w.device) for l in layers], dim=0)
+            hit = (tag, w, b, sc)
+            cache[key] = hit
+        return hit[1], hit[2], hit[3]
+
+    @staticmethod
+    def _mm(xq, w, b, xs, ws):
+        if b is not None:
+            return native.q8_mm_bias(xq, w, b, xs, ws, False, torch.bfloat16)
+        return native.q8_mm(xq, w, xs, ws, False, torch.bfloat16)
+
     @staticmethod
     def _quantize_once(x):
         """Hadamard (scale 1/sqrt(K)) + per-token INT8 quantizer of an activation, as q8_linear
@@ -75,26 +99,41 @@ class Attention(nn.Module):
             kq, ks = self._quantize_once(kv_src)
         else:
             kq, ks = hq, hs
-        query = self.to_q(hq, hs, out_dtype=mm_out_dtype)
-        key = self.to_k(kq, ks, out_dtype=mm_out_dtype)
-        value = self.to_v(kq, ks, out_dtype=mm_out_dtype)
-        batch_size = query.shape[0]
+        batch_size = hq.shape[0]
         heads = self.num_heads
         rope_here = encoder_hidden_states is None and self.use_rope
 
-        # Fast path: q/k norm + RoPE + per-head Hadamard + e4m3 cast as one kernel per tensor, straight
-        # into the attention kernel's operand layout (same roundings as the op-by-op path below).
+        # Fast path: projections that share an input run as ONE GEMM over row-stacked weights (same
+        # bits: every output column only sees its own weight row), and q/k norm + RoPE + per-head
+        # Hadamard + e4m3 cast are one kernel writing the attention kernel's operand layout (same
+        # roundings as the op-by-op path below).
         if (attn_type == "q8_kernels" and self.qk_rms_norm and self.head_dim == 64 and head_shard is None
-                and apply_qk_hadamard and query.dtype == torch.bfloat16 and non_mm_precision == torch.bfloat16
-                and query.dim() == 3 and (not rope_here or freqs_cis[0].shape[0] == 1)):
+                and apply_qk_hadamard and mm_out_dtype == torch.bfloat16 and non_mm_precision == torch.bfloat16
+                and hq.dim() == 3 and (not rope_here or freqs_cis[0].shape[0] == 1)):
             scale = math.sqrt(1 / 64) * math.sqrt(64 ** -0.5)
-            fc = freqs_cis if rope_here else None
-            q8_ = native.qk_norm_rope_prep(query, self.q_norm.weight, fc, heads, True, scale)
-            k8_ = native.qk_norm_rope_prep(key, self.k_norm.weight, fc, heads, True, scale)
-            vt8 = native.attention_prep_v(value.view(batch_size, -1, heads, self.head_dim).transpose(1, 2))
+            C = self.inner_dim
+            if encoder_hidden_states is None:
+                w, b, sc = self._stacked("qkv", (self.to_q, self.to_k, self.to_v))
+                qkv = self._mm(hq, w, b, hs, sc)
+                q8_, k8_ = native.qk_norm_rope_prep_pair(qkv[..., :C], qkv[..., C:2 * C], self.q_norm.weight,
+                                                         self.k_norm.weight, freqs_cis if rope_here else None, heads,
+                                                         True, scale)
+                value = qkv[..., 2 * C:]
+            else:
+                query = self.to_q(hq, hs, out_dtype=mm_out_dtype)
+                w, b, sc = self._stacked("kv", (self.to_k, self.to_v))
+                kv = self._mm(kq, w, b, ks, sc)
+                q8_ = native.qk_norm_rope_prep(query, self.q_norm.weight, None, heads, True, scale)
+                k8_ = native.qk_norm_rope_prep(kv[..., :C], self.k_norm.weight, None, heads, True, scale)
+                value = kv[..., C:]
+            vt8 = native.attention_prep_v(value.unflatten(-1, (heads, self.head_dim)).transpose(1, 2))
             hidden_states = native.flash_attention(q8_, k8_, vt8, 1.0, attention_mask, None, token_major_out=True)
             hidden_states = hidden_states.transpose(1, 2).reshape(batch_size, -1, heads * self.head_dim)
             return self._project_out(hidden_states, non_mm_precision, mm_out_dtype, out_gate, out_residual)
+
+        query = self.to_q(hq, hs, out_dtype=mm_out_dtype)
+        key = self.to_k(kq, ks, out_dtype=mm_out_dtype)
+        value = self.to_v(kq, ks, out_dtype=mm_out_dtype)
 
         if self.qk_rms_norm:
             query = self.q_norm(query, non_mm_precision)

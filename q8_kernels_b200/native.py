@@ -399,6 +399,41 @@ def qk_norm_rope_prep(x: torch.Tensor, norm_w: torch.Tensor, freqs_cis, num_head
     return out
 
 
+def qk_norm_rope_prep_pair(xq: torch.Tensor, xk: torch.Tensor, norm_wq: torch.Tensor, norm_wk: torch.Tensor, freqs_cis,
+                           num_heads: int, apply_hadamard: bool, qk_scale: float):
+    """qk_norm_rope_prep for the Q and K of one self-attention in a single launch (same shape and
+    strides, e.g. column slices of a fused projection output); returns (q8, k8), each e4m3 [B,H,S,64],
+    byte-identical to two separate calls."""
+    dev = require_cuda(xq, xk, norm_wq, norm_wk)
+    C = num_heads * 64
+    for x in (xq, xk):
+        if x.dtype != torch.bfloat16 or x.dim() != 3 or x.shape[2] != C or x.stride(2) != 1:
+            raise Q8KernelError("qk_norm_rope_prep_pair: inputs must be bfloat16 [B,S,H*64] with contiguous channels")
+    if xq.shape != xk.shape:
+        raise Q8KernelError("qk_norm_rope_prep_pair: q and k must have the same shape")
+    B, S, _ = xq.shape
+    ok = all(x.stride(0) == S * x.stride(1) and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0 for x in (xq, xk))
+    if not ok or xq.stride() != xk.stride():
+        xq, xk = xq.contiguous(), xk.contiguous()
+    cos = sin = None
+    if freqs_cis is not None:
+        cos, sin = freqs_cis
+        if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.numel() != S * C or sin.numel() != S * C:
+            raise Q8KernelError("qk_norm_rope_prep_pair: rotary tables must be float32 [1,S,H*64]")
+        cos, sin = cos.contiguous(), sin.contiguous()
+    for w in (norm_wq, norm_wk):
+        if w.dtype != torch.float32 or w.numel() != C:
+            raise Q8KernelError("qk_norm_rope_prep_pair: norm weights must be float32 [H*64]")
+    outq = torch.empty((B, num_heads, S, 64), dtype=E4M3, device=dev)
+    outk = torch.empty((B, num_heads, S, 64), dtype=E4M3, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_qk_norm_rope_prep_pair(ptr(xq), ptr(xk), xq.stride(1), ptr(norm_wq.contiguous()),
+                                             ptr(norm_wk.contiguous()), ptr(cos), ptr(sin), ptr(outq), ptr(outk), B, S,
+                                             num_heads, int(bool(apply_hadamard)), float(qk_scale), stream_ptr(dev)),
+              "qk_norm_rope_prep_pair")
+    return outq, outk
+
+
 def attention_prep_v(v: torch.Tensor) -> torch.Tensor:
     """V half of attention_prep: bf16 [B,H,S,64] view -> e4m3 [B,H,64,ceil16(S)] (transposed, zero padded)."""
     dev = require_cuda(v)

@@ -173,3 +173,18 @@ def test_attention_prep_v_alone_matches_attention_prep(nat, cuda_device):
     q, k, v = (t.to(cuda_device) for t in Hp.qkv(2, 3, 77, 64, seed=9))
     _, _, want = nat.attention_prep(q, k, v, False, 1.0)
     assert torch.equal(Hp.bits(nat.attention_prep_v(v)), Hp.bits(want))
+
+
+def test_paired_qk_prep_is_two_single_calls(nat, cuda_device):
+    """Q and K of a self-attention taken as column slices of one fused projection output."""
+    B, S, H = 2, 70, 32
+    C = H * 64
+    qkv = Hp.activations(B * S, 3 * C, seed=21).view(B, S, 3 * C).to(cuda_device)
+    wq = (1.0 + 0.1 * torch.randn(C, generator=Hp.gen(1))).to(cuda_device)
+    wk = (1.0 + 0.1 * torch.randn(C, generator=Hp.gen(2))).to(cuda_device)
+    ang = torch.rand(1, S, C, generator=Hp.gen(3)) * 6.28
+    fc = (ang.cos().to(cuda_device), ang.sin().to(cuda_device))
+    scale = 0.125 * math.sqrt(0.125)
+    q8, k8 = nat.qk_norm_rope_prep_pair(qkv[..., :C], qkv[..., C:2 * C], wq, wk, fc, H, True, scale)
+    assert torch.equal(Hp.bits(q8), Hp.bits(nat.qk_norm_rope_prep(qkv[..., :C], wq, fc, H, True, scale)))
+    assert torch.equal(Hp.bits(k8), Hp.bits(nat.qk_norm_rope_prep(qkv[..., C:2 * C], wk, fc, H, True, scale)))
