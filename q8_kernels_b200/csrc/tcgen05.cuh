@@ -77,13 +77,21 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t par
 // this wait exceeded kWaitLimitNs (in which case it raises *abort itself).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    // Slow path.  A failed try costs only the test and a counter; the abort flag and the clock are
+    // looked at once every 32 tries, so a waiting warp takes few issue slots from the working ones.
+    uint32_t tries = 0;
+    unsigned long long t0 = 0;
     for (;;) {
         if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
-        if (*abort != 0) return false;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) {
-            *abort = 1;
-            return false;
+        if ((++tries & 31u) == 0) {
+            if (*abort != 0) return false;
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
+                *abort = 1;
+                return false;
+            }
         }
     }
 }
