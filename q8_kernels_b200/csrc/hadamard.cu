@@ -151,6 +151,7 @@ struct PhaseLayout {
     static constexpr int C = 1 << LOG_C;
     static constexpr int G = 1 << B;
     static constexpr int BITS = B;
+    static constexpr int LOW = LO;
     static_assert(LO >= LOG_C, "group bits must lie above the run bits");
     __device__ static __forceinline__ int elem(int t, int j) {
         constexpr int LOWT = LO - LOG_C;
@@ -158,41 +159,56 @@ struct PhaseLayout {
     }
 };
 
-// registers (layout L) -> shared memory, natural element order (runs of 2 use float2 accesses
-// inside the swizzled float4 chunk)
+// Shared-memory exchange in natural element order, float4 chunks XOR-swizzled (swz4).  elem(t, j)
+// is a bitwise OR of disjoint bit fields and swz4 is linear over XOR, so the swizzled byte offset of
+// (t, j, k) is  offset(t) ^ offset(j, k)  with the second term a compile-time constant: one XOR per
+// access instead of re-deriving the swizzle.  Runs of 2 use float2 accesses inside the chunk (the
+// half-chunk select bit belongs to the thread term).
+template <typename L>
+__device__ __forceinline__ uint32_t exchange_thread_offset(int t) {
+    const int e = L::elem(t, 0);
+    uint32_t off = (uint32_t)swz4(e >> 2) << 4;
+    if constexpr (L::C < 4) off |= (uint32_t)((e >> 1) & 1) << 3;
+    return off;
+}
+template <typename L>
+__device__ __forceinline__ constexpr uint32_t exchange_const_offset(int j, int k) {
+    const int q = ((j << L::LOW) >> 2) + k;
+    return (uint32_t)(q ^ ((q >> 3) & 7)) << 4;
+}
+
+// registers (layout L) -> shared memory
 template <typename L, int V>
 __device__ __forceinline__ void exchange_write(float* xch, const float (&v)[V], int t) {
+    char* xb = reinterpret_cast<char*>(xch);
+    const uint32_t tb = exchange_thread_offset<L>(t);
 #pragma unroll
     for (int j = 0; j < L::G; ++j) {
-        const int e = L::elem(t, j);
         if constexpr (L::C >= 4) {
-            float4* x4 = reinterpret_cast<float4*>(xch);
 #pragma unroll
             for (int k = 0; k < L::C / 4; ++k)
-                x4[swz4((e >> 2) + k)] = make_float4(v[j * L::C + 4 * k], v[j * L::C + 4 * k + 1],
-                                                     v[j * L::C + 4 * k + 2], v[j * L::C + 4 * k + 3]);
+                *reinterpret_cast<float4*>(xb + (tb ^ exchange_const_offset<L>(j, k))) =
+                    make_float4(v[j * L::C + 4 * k], v[j * L::C + 4 * k + 1], v[j * L::C + 4 * k + 2], v[j * L::C + 4 * k + 3]);
         } else {
-            float2* x2 = reinterpret_cast<float2*>(xch);
-            x2[swz4(e >> 2) * 2 + ((e >> 1) & 1)] = make_float2(v[j * 2], v[j * 2 + 1]);
+            *reinterpret_cast<float2*>(xb + (tb ^ exchange_const_offset<L>(j, 0))) = make_float2(v[j * 2], v[j * 2 + 1]);
         }
     }
 }
 template <typename L, int V>
 __device__ __forceinline__ void exchange_read(const float* xch, float (&v)[V], int t) {
+    const char* xb = reinterpret_cast<const char*>(xch);
+    const uint32_t tb = exchange_thread_offset<L>(t);
 #pragma unroll
     for (int j = 0; j < L::G; ++j) {
-        const int e = L::elem(t, j);
         if constexpr (L::C >= 4) {
-            const float4* x4 = reinterpret_cast<const float4*>(xch);
 #pragma unroll
             for (int k = 0; k < L::C / 4; ++k) {
-                const float4 f = x4[swz4((e >> 2) + k)];
+                const float4 f = *reinterpret_cast<const float4*>(xb + (tb ^ exchange_const_offset<L>(j, k)));
                 v[j * L::C + 4 * k] = f.x; v[j * L::C + 4 * k + 1] = f.y;
                 v[j * L::C + 4 * k + 2] = f.z; v[j * L::C + 4 * k + 3] = f.w;
             }
         } else {
-            const float2* x2 = reinterpret_cast<const float2*>(xch);
-            const float2 f = x2[swz4(e >> 2) * 2 + ((e >> 1) & 1)];
+            const float2 f = *reinterpret_cast<const float2*>(xb + (tb ^ exchange_const_offset<L>(j, 0)));
             v[j * 2] = f.x; v[j * 2 + 1] = f.y;
         }
     }
@@ -271,10 +287,12 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
     constexpr int T = N / V;                                   // threads per row
     constexpr int ITEMS = V / 8;                               // 8-element input items per thread
     constexpr int R = LOG_N - LOG_V;                           // bits left after the register phase
-    constexpr int BMAX = LOG_V - 1;                            // keeps runs of >= 2 consecutive elements
-    constexpr int B1 = R < BMAX ? R : BMAX;
+    // one exchange when the bits fit (runs of >= 2 consecutive elements), else two balanced ones so
+    // that both keep runs of >= 4 (float4 accesses)
+    constexpr int BMAX = LOG_V - 1;
+    constexpr int B1 = R <= BMAX ? R : (R + 1) / 2;
     constexpr int B2 = R - B1;
-    static_assert(B2 <= BMAX, "row too long for this values-per-thread choice");
+    static_assert(B1 <= BMAX && B2 <= BMAX, "row too long for this values-per-thread choice");
     using L0 = PhaseLayout<LOG_V, 0, LOG_V>;                   // V consecutive elements
     using L1 = PhaseLayout<LOG_V, B1, LOG_V>;
     using L2 = PhaseLayout<LOG_V, B2, LOG_V + B1>;
@@ -308,9 +326,8 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
         const Item* stage = reinterpret_cast<const Item*>(xch);
 #pragma unroll
         for (int k = 0; k < ITEMS; ++k) {
-            const int item = t * ITEMS + k;
             union { Item raw; Tin e[8]; } u;
-            u.raw = stage[item ^ (t & (ITEMS - 1))];
+            u.raw = stage[(t * ITEMS + (t & (ITEMS - 1))) ^ k];   // == (t * ITEMS + k) ^ (t % ITEMS)
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[k * 8 + j] = to_float<Tin>(u.e[j]);
         }
@@ -403,7 +420,7 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
 #pragma unroll
             for (int i = 0; i < C; ++i) {
                 v[j * C + i] = round_through<Tin>(v[j * C + i]);
-                if (C <= 8 || LF::elem(t, j) + i < dim) m = fmaxf(m, fabsf(v[j * C + i]));
+                if (C <= 8 || LF::elem(t, j) + (i & ~7) < dim) m = fmaxf(m, fabsf(v[j * C + i]));
             }
             if (C > 8 || in) amax = fmaxf(amax, m);
         }
@@ -431,8 +448,12 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
                     using BV = typename ByteVec<PIECE>::type;
                     union { BV vec; uint8_t b[PIECE]; } u;
 #pragma unroll
-                    for (int i = 0; i < PIECE; ++i)
-                        u.b[i] = quantize_fast<Tout>(__fmul_rn(v[j * C + pc * PIECE + i], qmul));
+                    for (int i = 0; i < PIECE; i += 2) {
+                        const float2 y = fmul2(make_float2(v[j * C + pc * PIECE + i], v[j * C + pc * PIECE + i + 1]),
+                                               make_float2(qmul, qmul));
+                        u.b[i] = quantize_fast<Tout>(y.x);
+                        u.b[i + 1] = quantize_fast<Tout>(y.y);
+                    }
                     *reinterpret_cast<BV*>(reinterpret_cast<uint8_t*>(outr) + e + pc * PIECE) = u.vec;
                 }
             }
