@@ -124,6 +124,11 @@ def sweep_cases():
     return cases
 
 
+# DRAM traffic of the GEMM kernel per FLOP, from the ncu capture summarised in
+# profiles/gemm_fp8_pair_M6144_K2048_N8192_bias_gelu.md (29.6 MB read + 53.6 MB written, 206.158 GFLOP).
+NCU_DRAM_BYTES_PER_FLOP = (29.59e6 + 53.60e6) / 206.158e9
+
+
 def sweep_flops():
     return sum(2.0 * m * k * n for (m, k, n, _) in sweep_cases())
 
@@ -483,7 +488,11 @@ def main():
                     "api": "q8_kernels_b200.functional.linear.fp8_linear(bf16 pinned host activations) -> pinned host bf16; uploads, compute and downloads on three streams"},
             "gpu_launches": launches,
             "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": round(peak, 1), "unit": "TFLOP/s",
-                         "frac": round(per_gpu / peak, 4), "traffic": None,
+                         "frac": round(per_gpu / peak, 4),
+                         "traffic": round(NCU_DRAM_BYTES_PER_FLOP * flops / len(sweep_cases())),
+                         "traffic_basis": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the "
+                                          "M6144 K2048 N8192 bias+GELU launch (83.2 MB for 206.2 GFLOP), scaled by "
+                                          "FLOPs to the sweep's average launch",
                          "peak_basis": f"2 x {peaks['_source']} sustained dense bf16 cuBLAS rate "
                                        f"({peaks['bf16_tflops_sustained']} TFLOP/s); FP8 issues at twice the bf16 rate",
                          "frac_of_nominal_4500": round(per_gpu / 4500.0, 4),

@@ -130,19 +130,33 @@ __device__ __forceinline__ void store_vec(T* __restrict__ p, const float (&in)[N
     constexpr int BYTES = N * sizeof(T);
     if constexpr (BYTES <= 16) {
         using V = typename Vec<BYTES>::type;
-        union { V v; T e[N]; } u;
+        if constexpr (__is_same(T, __nv_bfloat16) && N % 2 == 0) {
+            union { V v; __nv_bfloat162 e2[N / 2]; } u;
 #pragma unroll
-        for (int i = 0; i < N; ++i) u.e[i] = from_float<T>(in[i]);
-        *reinterpret_cast<V*>(p) = u.v;
+            for (int i = 0; i < N; i += 2) u.e2[i / 2] = __floats2bfloat162_rn(in[i], in[i + 1]);
+            *reinterpret_cast<V*>(p) = u.v;
+        } else {
+            union { V v; T e[N]; } u;
+#pragma unroll
+            for (int i = 0; i < N; ++i) u.e[i] = from_float<T>(in[i]);
+            *reinterpret_cast<V*>(p) = u.v;
+        }
     } else {
         static_assert(BYTES % 16 == 0, "vector width");
         constexpr int PER = 16 / sizeof(T);
 #pragma unroll
         for (int c = 0; c < BYTES / 16; ++c) {
-            union { uint4 v; T e[PER]; } u;
+            if constexpr (sizeof(T) == 2 && __is_same(T, __nv_bfloat16)) {
+                union { uint4 v; __nv_bfloat162 e2[4]; } u;    // packed conversions, same rounding
 #pragma unroll
-            for (int i = 0; i < PER; ++i) u.e[i] = from_float<T>(in[c * PER + i]);
-            reinterpret_cast<uint4*>(p)[c] = u.v;
+                for (int i = 0; i < 8; i += 2) u.e2[i / 2] = __floats2bfloat162_rn(in[c * 8 + i], in[c * 8 + i + 1]);
+                reinterpret_cast<uint4*>(p)[c] = u.v;
+            } else {
+                union { uint4 v; T e[PER]; } u;
+#pragma unroll
+                for (int i = 0; i < PER; ++i) u.e[i] = from_float<T>(in[c * PER + i]);
+                reinterpret_cast<uint4*>(p)[c] = u.v;
+            }
         }
     }
 }

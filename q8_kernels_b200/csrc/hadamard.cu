@@ -55,6 +55,18 @@ template <typename T> __device__ __forceinline__ float round_through(float v) {
     return to_float<T>(from_float<T>(v));
 }
 
+// Two values at once: for bf16 one packed conversion (an ALU-pipe F2FP instead of two conversions on
+// the 16-lane special-function unit) and two bit operations to widen the halves again.
+template <typename T> __device__ __forceinline__ float2 round_through2(float a, float b) {
+    if constexpr (std::is_same_v<T, __nv_bfloat16>) {
+        const __nv_bfloat162 p = __floats2bfloat162_rn(a, b);  // a in the low half
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&p);
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    } else {
+        return make_float2(round_through<T>(a), round_through<T>(b));
+    }
+}
+
 template <typename Tq> __device__ __forceinline__ uint8_t quantize_one(float y) {
     if constexpr (std::is_same_v<Tq, int8_t>) return (uint8_t)(int8_t)(int)roundf(y);
     else return float_to_e4m3_c10(y);
@@ -70,10 +82,17 @@ template <> struct ByteVec<16> { using type = uint4; };
 template <typename T, int N>
 __device__ __forceinline__ void store_elems(T* p, const float (&v)[N]) {
     using V = typename ByteVec<N * sizeof(T)>::type;
-    union { V vec; T e[N]; } u;
+    if constexpr (std::is_same_v<T, __nv_bfloat16> && N % 2 == 0) {
+        union { V vec; __nv_bfloat162 e2[N / 2]; } u;          // packed conversions, same rounding
 #pragma unroll
-    for (int i = 0; i < N; ++i) u.e[i] = from_float<T>(v[i]);
-    *reinterpret_cast<V*>(p) = u.vec;
+        for (int i = 0; i < N; i += 2) u.e2[i / 2] = __floats2bfloat162_rn(v[i], v[i + 1]);
+        *reinterpret_cast<V*>(p) = u.vec;
+    } else {
+        union { V vec; T e[N]; } u;
+#pragma unroll
+        for (int i = 0; i < N; ++i) u.e[i] = from_float<T>(v[i]);
+        *reinterpret_cast<V*>(p) = u.vec;
+    }
 }
 
 template <typename Tq, int N>
@@ -359,11 +378,18 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
                 load_vec<__nv_bfloat16, 8>(sc + k * 8, s8);
                 load_vec<__nv_bfloat16, 8>(sh + k * 8, h8);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float n = round_through<__nv_bfloat16>(__fmul_rn(v[k * 8 + j], rr));
-                    const float m1 = round_through<__nv_bfloat16>(__fadd_rn(1.0f, s8[j]));
-                    const float tm = round_through<__nv_bfloat16>(__fmul_rn(n, m1));
-                    v[k * 8 + j] = round_through<__nv_bfloat16>(__fadd_rn(tm, h8[j]));
+                for (int j = 0; j < 8; j += 2) {
+                    using BF = __nv_bfloat16;
+                    const float2 xr2 = fmul2(make_float2(v[k * 8 + j], v[k * 8 + j + 1]), make_float2(rr, rr));
+                    const float2 n = round_through2<BF>(xr2.x, xr2.y);
+                    const float2 s1 = fadd2(make_float2(1.0f, 1.0f), make_float2(s8[j], s8[j + 1]));
+                    const float2 m1 = round_through2<BF>(s1.x, s1.y);
+                    const float2 nm = fmul2(n, m1);
+                    const float2 tm = round_through2<BF>(nm.x, nm.y);
+                    const float2 th = fadd2(tm, make_float2(h8[j], h8[j + 1]));
+                    const float2 u = round_through2<BF>(th.x, th.y);
+                    v[k * 8 + j] = u.x;
+                    v[k * 8 + j + 1] = u.y;
                 }
             }
         }
@@ -418,9 +444,11 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
             const bool in = LF::elem(t, j) < dim;              // dim % 8 == 0: a run of <= 8 is all in or all out
             float m = 0.f;
 #pragma unroll
-            for (int i = 0; i < C; ++i) {
-                v[j * C + i] = round_through<Tin>(v[j * C + i]);
-                if (C <= 8 || LF::elem(t, j) + (i & ~7) < dim) m = fmaxf(m, fabsf(v[j * C + i]));
+            for (int i = 0; i < C; i += 2) {
+                const float2 rt = round_through2<Tin>(v[j * C + i], v[j * C + i + 1]);
+                v[j * C + i] = rt.x;
+                v[j * C + i + 1] = rt.y;
+                if (C <= 8 || LF::elem(t, j) + (i & ~7) < dim) m = fmaxf(m, fmaxf(fabsf(rt.x), fabsf(rt.y)));
             }
             if (C > 8 || in) amax = fmaxf(amax, m);
         }
