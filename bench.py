@@ -378,9 +378,20 @@ def bench_detail(q8, dev, peaks, steps):
         tproj = stack.caption_projection(text)
         blk = stack.transformer_blocks[0]
         ms_blk = timed(lambda: blk(x, freqs, None, tproj, lens, ts, attn_type="q8_kernels"), 10)
+        # the same stack replayed from one CUDA graph (no per-launch host work between its ~730 kernels)
+        side = torch.cuda.Stream(dev)
+        with torch.cuda.stream(side):
+            stack(x, grid, text, lens, ts, attn_type="q8_kernels")
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graphed_out = stack(x, grid, text, lens, ts, attn_type="q8_kernels")   # noqa: F841
+        ms_stack_graph = timed(graph.replay, 3)
+        del graph, graphed_out
     flop_blk = 2.0 * S * (6 * 2048 ** 2 + 2 * 2048 * 8192) + 2.0 * T * 2 * 2048 ** 2 + 4.0 * 32 * S * S * 64 \
         + 4.0 * 32 * S * T * 64
     out["dit"] = {"block_ms": round(ms_blk, 4), "stack28_ms": round(ms_stack, 3),
+                  "stack28_cuda_graph_ms": round(ms_stack_graph, 3),
                   "block_tflops": round(flop_blk / ms_blk / 1e9, 1), "tokens": S, "text_tokens": T,
                   "linears": "int8", "attention": "fp8 hadamard"}
     return out

@@ -588,6 +588,13 @@ attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bf
     const int64_t b = row / S;
     float v[8];
     load_vec<__nv_bfloat16, 8>(x + row * x_row_stride + t * 8, v);
+    // the weight and rotary rows do not depend on the reduction: fetch them under its latency
+    float wv[8], c[8], sn[8];
+    load_vec<float, 8>(norm_w + t * 8, wv);
+    if (cos_t != nullptr) {
+        load_vec<float, 8>(cos_t + (int64_t)s_idx * dim + t * 8, c);
+        load_vec<float, 8>(sin_t + (int64_t)s_idx * dim + t * 8, sn);
+    }
 
     float ss = 0.f;
 #pragma unroll
@@ -599,16 +606,12 @@ attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bf
     for (int w = 1; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
     const float r = rsqrtf(tot * (1.0f / (float)dim));
 
-    float wv[8];
-    load_vec<float, 8>(norm_w + t * 8, wv);
 #pragma unroll
     for (int j = 0; j < 8; ++j)
         v[j] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v[j], r), wv[j])));
 
     if (cos_t != nullptr) {
-        float c[8], sn[8], o[8];
-        load_vec<float, 8>(cos_t + (int64_t)s_idx * dim + t * 8, c);
-        load_vec<float, 8>(sin_t + (int64_t)s_idx * dim + t * 8, sn);
+        float o[8];
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
             o[j]     = __fadd_rn(__fmul_rn(-v[j + 1], sn[j]), __fmul_rn(v[j], c[j]));

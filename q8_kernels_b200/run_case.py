@@ -31,6 +31,7 @@ def main() -> None:
     ap.add_argument("--dim", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--graph", action="store_true", help="capture the case into a CUDA graph and time its replays")
     a = ap.parse_args()
 
     import q8_kernels_b200 as q8
@@ -99,6 +100,17 @@ def main() -> None:
     for _ in range(a.warmup):
         fn()
     torch.cuda.synchronize()
+    if a.graph:
+        side = torch.cuda.Stream(dev)
+        with torch.cuda.stream(side):                     # first calls outside capture: lazy set-up, allocator warm-up
+            fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            keep = fn()                                   # noqa: F841  (outputs live in the graph's pool)
+        fn = graph.replay
+        fn()
+        torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
     for _ in range(a.iters):
