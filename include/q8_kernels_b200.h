@@ -116,6 +116,20 @@ Q8K_API int q8k_fma_8bit(const void* x, const void* y, int y_dtype, const void* 
 Q8K_API int q8k_gelu_forward(const void* x, int x_dtype, void* out, int out_dtype, int64_t rows, int dim,
                      void* stream);
 
+/* Training-side gradients of the row-wise ops (forward-only users never call these).  The incoming
+ * gradient is read in the OUTPUT dtype, as the reference's kernels do.
+ *   gelu_backward:     csrc/ops/gelu_act.cpp:84-129, gelu_backward_cuda.cu:88-100
+ *   rope_backward:     csrc/ops/rope.cpp:150-199, rope_backward_cuda.cu:101-110 (freq_rows as in q8k_rope)
+ *   rms_norm_backward: csrc/ops/rms_norm.cpp:157-214, rms_norm_backward_cuda.cu:135-160; x_normed is the
+ *                      forward output, x_norms the per-row rsqrt it returned, weights fp32 or NULL     */
+Q8K_API int q8k_gelu_backward(const void* x, int x_dtype, const void* grad_out, void* out, int out_dtype,
+                      int64_t rows, int dim, void* stream);
+Q8K_API int q8k_rope_backward(const void* grad_out, int grad_dtype, const float* cos_freqs, const float* sin_freqs,
+                      void* out, int out_dtype, int64_t rows, int dim, int64_t freq_rows, void* stream);
+Q8K_API int q8k_rms_norm_backward(const void* x_normed, int x_dtype, const float* x_norms, const void* grad_out,
+                          const float* weights, void* out, int out_dtype, int64_t rows, int dim,
+                          void* stream);
+
 /* 8-bit GEMM  C[b] = act((A[b] . B[b]^T) * (sa[m]*sb[n]) + bias[n]).
  * A [bs_a, M, K], B [bs_b, N, K] K-contiguous int8 (q8k_q8_mm) or e4m3
  * (q8k_fp8_mm); bs_a == bs_b or one of them 1; sa [bs_a, M], sb [bs_b, N],

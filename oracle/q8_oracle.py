@@ -244,6 +244,56 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
     return cast_out(out, out_dtype)
 
 
+# --------------------------------------------------------------------------- training-side gradients
+
+def gelu_backward(x: torch.Tensor, grad_output: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """csrc/ops/gelu_backward_cuda.cu:88-100: with tau = k (x + f x x x), phi = tanh(tau),
+    phi' = (1 - phi^2) k (1 + 3 f x^2):  out = g (0.5 (1 + phi) + 0.5 x phi'), fp32, g read in the
+    output dtype."""
+    if out_dtype is None:
+        out_dtype = x.dtype
+    k, f = 0.7978845608028654, 0.044715
+    v = x.to(torch.float32)
+    g = grad_output.to(out_dtype).to(torch.float32)
+    f32 = lambda c: torch.tensor(c, dtype=torch.float32)  # noqa: E731
+    tau = f32(k) * (v + f32(f) * v * v * v)
+    phi = torch.tanh(tau)
+    phi_prime = (1.0 - phi * phi) * (f32(k) * (1.0 + (f32(f) * f32(3.0)) * v * v))
+    return cast_out(g * (0.5 * (1.0 + phi) + 0.5 * v * phi_prime), out_dtype)
+
+
+def rope_backward(grad_out: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """csrc/ops/rope_backward_cuda.cu:101-110: ``o[2i] = g[2i] c[2i] + g[2i+1] s[2i+1]``,
+    ``o[2i+1] = -g[2i] s[2i] + g[2i+1] c[2i+1]``, each product rounded to fp32 before the add."""
+    if out_dtype is None:
+        out_dtype = grad_out.dtype
+    g = grad_out.to(torch.float32)
+    g0, g1 = g[..., 0::2], g[..., 1::2]
+    c0, c1 = cos[..., 0::2].float(), cos[..., 1::2].float()
+    s0, s1 = sin[..., 0::2].float(), sin[..., 1::2].float()
+    o0 = g0 * c0 + g1 * s1
+    o1 = (-g0) * s0 + g1 * c1
+    return cast_out(torch.stack((o0, o1), dim=-1).reshape(grad_out.shape), out_dtype)
+
+
+def rms_norm_backward(x_normed: torch.Tensor, x_norms: torch.Tensor, grad_out: torch.Tensor,
+                      weights: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """csrc/ops/rms_norm_backward_cuda.cu:135-160: ``r / dim * (dim g_i w_i - y_i / w_i * sum_j g_j y_j)``
+    with y the forward output, r the saved per-row rsqrt, g read in the output dtype; the row sum is
+    taken in float64 here (the kernel's fp32 summation order is not part of the semantics)."""
+    if out_dtype is None:
+        out_dtype = x_normed.dtype
+    dim = x_normed.shape[-1]
+    y = x_normed.to(torch.float32)
+    g = grad_out.to(out_dtype).to(torch.float32)
+    w = torch.ones(dim, dtype=torch.float32) if weights is None else weights.to(torch.float32)
+    dot = (g.to(torch.float64) * y.to(torch.float64)).sum(dim=-1, keepdim=True).to(torch.float32)
+    fdim = torch.tensor(float(dim), dtype=torch.float32)
+    r = x_norms.to(torch.float32).unsqueeze(-1) / fdim
+    return cast_out(r * (fdim * g * w - y / w * dot), out_dtype)
+
+
 def apply_rotary_emb_torch(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     """The pure-torch path the reference's ``apply_rope`` actually runs
     (q8_kernels/functional/rope.py:27-43); result dtype follows torch promotion."""

@@ -7,6 +7,6 @@ Importing the package loads ``libq8k_b200.so`` (built by
 or eager fallback.
 """
 from . import _lib, native  # noqa: F401  (loads the native library, fails loudly if absent)
-from . import functional, modules, blocks  # noqa: F401
+from . import functional, modules, blocks, utils, graph  # noqa: F401
 
 __version__ = "0.1.0"

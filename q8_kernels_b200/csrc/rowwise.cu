@@ -10,6 +10,7 @@
 //
 // No fast-math: the quantizer must reproduce IEEE division and C round().
 
+#include <type_traits>
 #include "common.cuh"
 
 namespace q8k {
@@ -201,6 +202,94 @@ gelu_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, int dim) {
     store_vec<Tout, kItem>(out + row * (int64_t)dim + e, o);
 }
 
+// ------------------------------------------------------------------ training-side gradients
+// gelu_backward_kernel (csrc/ops/gelu_backward_cuda.cu:88-100): d/dx of the tanh GELU times the
+// incoming gradient, all in fp32, same association of the products as the reference.
+template <typename Tx, typename Tg, typename Tout, int T>
+__global__ void __launch_bounds__(T)
+gelu_backward_kernel(const Tx* __restrict__ x, const Tg* __restrict__ grad, Tout* __restrict__ out, int dim) {
+    const int64_t row = blockIdx.x;
+    const int e = (blockIdx.y * T + threadIdx.x) * kItem;
+    if (e >= dim) return;
+    float xv[kItem], gv[kItem], o[kItem];
+    load_vec<Tx, kItem>(x + row * (int64_t)dim + e, xv);
+    load_vec<Tg, kItem>(grad + row * (int64_t)dim + e, gv);
+    constexpr float k = 0.7978845608028654f, f = 0.044715f;
+#pragma unroll
+    for (int j = 0; j < kItem; ++j) {
+        const float v = xv[j];
+        const float tau = k * (v + f * v * v * v);
+        const float phi = tanhf(tau);
+        const float phi_prime = (1.0f - phi * phi) * (k * (1.0f + f * 3.0f * v * v));
+        o[j] = gv[j] * (0.5f * (1.0f + phi) + 0.5f * v * phi_prime);
+    }
+    store_vec<Tout, kItem>(out + row * (int64_t)dim + e, o);
+}
+
+// rope_backward_kernel (csrc/ops/rope_backward_cuda.cu:101-110): the transposed rotation.
+template <typename Tg, typename Tout, int T>
+__global__ void __launch_bounds__(T)
+rope_backward_kernel(const Tg* __restrict__ grad, const float* __restrict__ cosf_, const float* __restrict__ sinf_,
+                     Tout* __restrict__ out, int dim, int64_t freq_rows) {
+    const int64_t row = blockIdx.x;
+    const int e = (blockIdx.y * T + threadIdx.x) * kItem;
+    if (e >= dim) return;
+    const int64_t frow = freq_rows > 0 ? row % freq_rows : row;
+    float g[kItem], c[kItem], s[kItem], o[kItem];
+    load_vec<Tg, kItem>(grad + row * (int64_t)dim + e, g);
+    load_vec<float, kItem>(cosf_ + frow * (int64_t)dim + e, c);
+    load_vec<float, kItem>(sinf_ + frow * (int64_t)dim + e, s);
+#pragma unroll
+    for (int j = 0; j < kItem; j += 2) {
+        o[j]     = __fadd_rn(__fmul_rn(g[j], c[j]), __fmul_rn(g[j + 1], s[j + 1]));
+        o[j + 1] = __fadd_rn(__fmul_rn(-g[j], s[j]), __fmul_rn(g[j + 1], c[j + 1]));
+    }
+    store_vec<Tout, kItem>(out + row * (int64_t)dim + e, o);
+}
+
+// rms_norm_backward_kernel (csrc/ops/rms_norm_backward_cuda.cu:135-160): with y the forward
+// output (weights included), r the saved rsqrt(mean x^2) and g the incoming gradient,
+//   dx_i = r / dim * (dim * g_i * w_i - y_i / w_i * sum_j g_j y_j).
+template <typename Ty, typename Tg, typename Tout, int ITEMS, int T>
+__global__ void __launch_bounds__(T)
+rms_norm_backward_kernel(const Ty* __restrict__ y, const float* __restrict__ rrms, const Tg* __restrict__ grad,
+                         const float* __restrict__ w, Tout* __restrict__ out, int dim) {
+    __shared__ float red[32];
+    const int64_t row = blockIdx.x;
+    float yv[ITEMS][kItem], gv[ITEMS][kItem];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int e = (threadIdx.x + i * T) * kItem;
+        if (e < dim) {
+            load_vec<Ty, kItem>(y + row * (int64_t)dim + e, yv[i]);
+            load_vec<Tg, kItem>(grad + row * (int64_t)dim + e, gv[i]);
+#pragma unroll
+            for (int j = 0; j < kItem; ++j) dot = fmaf(gv[i][j], yv[i][j], dot);
+        }
+    }
+    dot = block_reduce_sum<T>(dot, red);
+    const float fdim = (float)dim;
+    const float r_over_dim = rrms[row] / fdim;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int e = (threadIdx.x + i * T) * kItem;
+        if (e < dim) {
+            float wv[kItem], o[kItem];
+            if (w != nullptr) {
+                load_vec<float, kItem>(w + e, wv);
+            } else {
+#pragma unroll
+                for (int j = 0; j < kItem; ++j) wv[j] = 1.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < kItem; ++j)
+                o[j] = r_over_dim * (fdim * gv[i][j] * wv[j] - yv[i][j] / wv[j] * dot);
+            store_vec<Tout, kItem>(out + row * (int64_t)dim + e, o);
+        }
+    }
+}
+
 // ------------------------------------------------------------------ launch helpers
 template <typename Tin, typename Tout>
 static int launch_quant(const void* x, void* q, float* scales, int64_t rows, int dim,
@@ -356,6 +445,100 @@ extern "C" int q8k_gelu_forward(const void* x, int x_dtype, void* out, int out_d
     else if (x_dtype == Q8K_DT_E4M3 && out_dtype == Q8K_DT_E4M3) Q8K_GELU(e4m3_t, e4m3_t);
     else { set_error_detail("gelu_forward: dtype pair (%d -> %d) not supported", x_dtype, out_dtype); return Q8K_ERR_UNSUPPORTED; }
 #undef Q8K_GELU
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+// ------------------------------------------------------------------ gradients (training side)
+namespace q8k {
+template <typename F>
+static int dispatch_8bit_pair(const char* op, int a_dtype, int b_dtype, F&& f) {
+    // calls f(type tag of a, type tag of b) for a, b in {bf16, e4m3}
+    if (a_dtype == Q8K_DT_BF16 && b_dtype == Q8K_DT_BF16) return f((__nv_bfloat16*)nullptr, (__nv_bfloat16*)nullptr);
+    if (a_dtype == Q8K_DT_BF16 && b_dtype == Q8K_DT_E4M3) return f((__nv_bfloat16*)nullptr, (e4m3_t*)nullptr);
+    if (a_dtype == Q8K_DT_E4M3 && b_dtype == Q8K_DT_BF16) return f((e4m3_t*)nullptr, (__nv_bfloat16*)nullptr);
+    if (a_dtype == Q8K_DT_E4M3 && b_dtype == Q8K_DT_E4M3) return f((e4m3_t*)nullptr, (e4m3_t*)nullptr);
+    set_error_detail("%s: dtype pair (%d, %d) not supported (bf16 / e4m3 only)", op, a_dtype, b_dtype);
+    return Q8K_ERR_UNSUPPORTED;
+}
+}  // namespace q8k
+
+extern "C" int q8k_gelu_backward(const void* x, int x_dtype, const void* grad_out, void* out, int out_dtype,
+                                 int64_t rows, int dim, void* stream) {
+    const char* op = "gelu_backward";
+    if (int rc = check_rows_dim(op, rows, dim, 16)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(x && grad_out && out, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE(aligned16(x) && aligned16(grad_out) && aligned16(out), Q8K_ERR_INVALID_ARG,
+                "%s: pointers must be 16-byte aligned", op);
+    cudaStream_t st = (cudaStream_t)stream;
+    constexpr int T = 128;
+    dim3 grid((unsigned)rows, (unsigned)((dim / kItem + T - 1) / T));
+    // the incoming gradient has the output's dtype (csrc/ops/gelu_backward_cuda.cu:83)
+    int rc = dispatch_8bit_pair(op, x_dtype, out_dtype, [&](auto* tx, auto* to) {
+        using Tx = std::remove_pointer_t<decltype(tx)>;
+        using To = std::remove_pointer_t<decltype(to)>;
+        gelu_backward_kernel<Tx, To, To, T><<<grid, T, 0, st>>>((const Tx*)x, (const To*)grad_out, (To*)out, dim);
+        return Q8K_OK;
+    });
+    if (rc) return rc;
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_rope_backward(const void* grad_out, int grad_dtype, const float* cos_freqs, const float* sin_freqs,
+                                 void* out, int out_dtype, int64_t rows, int dim, int64_t freq_rows, void* stream) {
+    const char* op = "rope_backward";
+    if (int rc = check_rows_dim(op, rows, dim, 16)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(grad_out && out && cos_freqs && sin_freqs, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE(aligned16(grad_out) && aligned16(out) && aligned16(cos_freqs) && aligned16(sin_freqs),
+                Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
+    Q8K_REQUIRE(freq_rows >= 0, Q8K_ERR_INVALID_ARG, "%s: freq_rows must be >= 0", op);
+    cudaStream_t st = (cudaStream_t)stream;
+    constexpr int T = 128;
+    dim3 grid((unsigned)rows, (unsigned)((dim / kItem + T - 1) / T));
+    int rc = dispatch_8bit_pair(op, grad_dtype, out_dtype, [&](auto* tg, auto* to) {
+        using Tg = std::remove_pointer_t<decltype(tg)>;
+        using To = std::remove_pointer_t<decltype(to)>;
+        rope_backward_kernel<Tg, To, T><<<grid, T, 0, st>>>((const Tg*)grad_out, cos_freqs, sin_freqs, (To*)out, dim, freq_rows);
+        return Q8K_OK;
+    });
+    if (rc) return rc;
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_rms_norm_backward(const void* x_normed, int x_dtype, const float* x_norms, const void* grad_out,
+                                     const float* weights, void* out, int out_dtype, int64_t rows, int dim,
+                                     void* stream) {
+    const char* op = "rms_norm_backward";
+    if (int rc = check_rows_dim(op, rows, dim, 16)) return rc;
+    if (rows == 0) return Q8K_OK;
+    Q8K_REQUIRE(x_normed && x_norms && grad_out && out, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE(aligned16(x_normed) && aligned16(grad_out) && aligned16(out) && aligned16(weights), Q8K_ERR_INVALID_ARG,
+                "%s: pointers must be 16-byte aligned", op);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int items = dim / kItem;
+    if (items > 4096) { set_error_detail("%s: dim %d exceeds 32768", op, dim); return Q8K_ERR_UNSUPPORTED; }
+    // the incoming gradient has the output's dtype (csrc/ops/rms_norm_backward_cuda.cu:117)
+    int rc = dispatch_8bit_pair(op, x_dtype, out_dtype, [&](auto* ty, auto* to) {
+        using Ty = std::remove_pointer_t<decltype(ty)>;
+        using To = std::remove_pointer_t<decltype(to)>;
+#define Q8K_RB_LAUNCH(ITEMS, T)                                                                   \
+    rms_norm_backward_kernel<Ty, To, To, ITEMS, T><<<(unsigned)rows, T, 0, st>>>(                   \
+        (const Ty*)x_normed, x_norms, (const To*)grad_out, weights, (To*)out, dim)
+        if (items <= 32)        Q8K_RB_LAUNCH(1, 32);
+        else if (items <= 128)  Q8K_RB_LAUNCH(1, 128);
+        else if (items <= 256)  Q8K_RB_LAUNCH(2, 128);
+        else if (items <= 512)  Q8K_RB_LAUNCH(4, 128);
+        else if (items <= 1024) Q8K_RB_LAUNCH(4, 256);
+        else if (items <= 2048) Q8K_RB_LAUNCH(8, 256);
+        else                    Q8K_RB_LAUNCH(8, 512);
+#undef Q8K_RB_LAUNCH
+        return Q8K_OK;
+    });
+    if (rc) return rc;
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }

@@ -209,6 +209,79 @@ def gelu_forward(x: torch.Tensor, out_type: Optional[torch.dtype] = None) -> tor
     return out.reshape(shape)
 
 
+def gelu_backward(x: torch.Tensor, grad_output: torch.Tensor, out_type: Optional[torch.dtype] = None) -> torch.Tensor:
+    """csrc/ops/gelu_act.cpp:84-129: ``grad_output * d gelu_tanh(x) / dx``.  The reference kernel reads
+    ``grad_output`` in the output dtype; a gradient of another dtype is cast to it first."""
+    dev = require_cuda(x, grad_output)
+    if grad_output.shape != x.shape:
+        raise Q8KernelError("gelu_backward: grad_output and x shapes differ")
+    out_type = x.dtype if out_type is None else out_type
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1]).contiguous()
+    g2 = grad_output.reshape(-1, shape[-1]).to(out_type).contiguous()
+    out = torch.empty(x2.shape, dtype=out_type, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_gelu_backward(ptr(x2), dt(x2.dtype), ptr(g2), ptr(out), dt(out_type), x2.shape[0], x2.shape[1],
+                                    stream_ptr(dev)), "gelu_backward")
+    return out.reshape(shape)
+
+
+def rope_backward(grad_out: torch.Tensor, cos_freqs: torch.Tensor, sin_freqs: torch.Tensor,
+                  out_type: Optional[torch.dtype] = None) -> torch.Tensor:
+    """csrc/ops/rope.cpp:150-199: the transposed rotation applied to the incoming gradient."""
+    dev = require_cuda(grad_out, cos_freqs, sin_freqs)
+    if cos_freqs.dtype != torch.float32 or sin_freqs.dtype != torch.float32:
+        raise Q8KernelError("rope_backward: cos/sin tables must be float32")
+    if cos_freqs.shape != sin_freqs.shape:
+        raise Q8KernelError("rope_backward: cos and sin shapes differ")
+    out_type = grad_out.dtype if out_type is None else out_type
+    shape = grad_out.shape
+    dim = shape[-1]
+    g2 = grad_out.reshape(-1, dim).contiguous()
+    rows = g2.shape[0]
+    c2 = cos_freqs.reshape(-1, dim).contiguous()
+    s2 = sin_freqs.reshape(-1, dim).contiguous()
+    if c2.shape[0] == rows:
+        freq_rows = 0
+    elif rows % c2.shape[0] == 0 and cos_freqs.dim() == grad_out.dim() and cos_freqs.shape[0] == 1:
+        freq_rows = c2.shape[0]
+    else:
+        raise Q8KernelError(f"rope_backward: table shape {tuple(cos_freqs.shape)} does not match {tuple(shape)}")
+    out = torch.empty((rows, dim), dtype=out_type, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_rope_backward(ptr(g2), dt(g2.dtype), ptr(c2), ptr(s2), ptr(out), dt(out_type), rows, dim,
+                                    freq_rows, stream_ptr(dev)), "rope_backward")
+    return out.reshape(shape)
+
+
+def rms_norm_backward(x_normed: torch.Tensor, x_norms: torch.Tensor, grad_out: torch.Tensor,
+                      weights: Optional[torch.Tensor] = None, out_type: Optional[torch.dtype] = None) -> torch.Tensor:
+    """csrc/ops/rms_norm.cpp:157-214: gradient w.r.t. the input of ``rms_norm`` from its saved output
+    ``x_normed`` and per-row ``x_norms``.  ``grad_out`` is read in the output dtype, as in the reference."""
+    dev = require_cuda(x_normed, x_norms, grad_out, weights)
+    if weights is not None and weights.dtype != torch.float32:
+        raise Q8KernelError("rms_norm_backward: weights must be float32")
+    if grad_out.shape != x_normed.shape:
+        raise Q8KernelError("rms_norm_backward: grad_out and x_normed shapes differ")
+    out_type = x_normed.dtype if out_type is None else out_type
+    shape = x_normed.shape
+    y2 = x_normed.reshape(-1, shape[-1]).contiguous()
+    g2 = grad_out.reshape(-1, shape[-1]).to(out_type).contiguous()
+    rows, dim = y2.shape
+    r = x_norms.reshape(-1).to(torch.float32).contiguous()
+    if r.numel() != rows:
+        raise Q8KernelError("rms_norm_backward: x_norms must hold one value per row")
+    if weights is not None:
+        weights = weights.contiguous()
+        if weights.numel() != dim:
+            raise Q8KernelError("rms_norm_backward: weights size does not match the last dim")
+    out = torch.empty((rows, dim), dtype=out_type, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_rms_norm_backward(ptr(y2), dt(y2.dtype), ptr(r), ptr(g2), ptr(weights), ptr(out), dt(out_type),
+                                        rows, dim, stream_ptr(dev)), "rms_norm_backward")
+    return out.reshape(shape)
+
+
 # ---------------------------------------------------------------- gemm._C
 
 def _gemm(fn, name, a, b, bias, a_scales, b_scales, fuse_gelu, out_type, in_dtype):

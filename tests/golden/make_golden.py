@@ -8,7 +8,9 @@ Two kinds of file:
   path the reference really runs) and ``precompute_freqs_cis``
   (q8_kernels/models/LTXVideo.py:86-148).  Their native and diffusers imports
   are replaced by inert stubs; only torch arithmetic of the reference executes.
-  These pin the oracle's RoPE and RoPE-table restatements.
+  These pin the oracle's RoPE and RoPE-table restatements.  ``ref_convert_state_dict.npz`` is the
+  reference's checkpoint converter (q8_kernels/utils/convert_weights.py:23-78) run on a miniature
+  diffusers-style state dict with its Hadamard / quantizer calls served by the oracle.
 * ``oracle_*.npz`` -- small seeded cases run through oracle/q8_oracle.py, kept
   so that the GPU kernels are also checked against frozen vectors and a change
   of the oracle shows up as a diff.  The reference has no tests or vectors for
@@ -97,6 +99,59 @@ def reference_fixtures() -> None:
     print("reference fixtures:", tuple(cos.shape), out.dtype)
 
 
+def synthetic_checkpoint(hidden: int = 64, ffn: int = 256, caption: int = 32, blocks: int = 2, seed: int = 77):
+    """A diffusers-style LTX-Video transformer state dict in miniature (same key names, bf16)."""
+    g = torch.Generator().manual_seed(seed)
+    rnd = lambda *shape: (torch.randn(*shape, generator=g) * 0.05).to(torch.bfloat16)  # noqa: E731
+    sd = {}
+    for b in range(blocks):
+        pre = f"transformer_blocks.{b}."
+        for attn, kv in (("attn1", hidden), ("attn2", hidden)):
+            for proj, k in (("to_q", hidden), ("to_k", kv), ("to_v", kv), ("to_out.0", hidden)):
+                sd[f"{pre}{attn}.{proj}.weight"] = rnd(hidden, k)
+                sd[f"{pre}{attn}.{proj}.bias"] = rnd(hidden)
+            sd[f"{pre}{attn}.q_norm.weight"] = 1 + rnd(hidden)
+            sd[f"{pre}{attn}.k_norm.weight"] = 1 + rnd(hidden)
+        sd[f"{pre}ff.net.0.proj.weight"] = rnd(ffn, hidden)
+        sd[f"{pre}ff.net.0.proj.bias"] = rnd(ffn)
+        sd[f"{pre}ff.net.2.weight"] = rnd(hidden, ffn)
+        sd[f"{pre}ff.net.2.bias"] = rnd(hidden)
+        sd[f"{pre}scale_shift_table"] = rnd(6, hidden)
+    sd["patchify_proj.weight"] = rnd(hidden, 16)
+    sd["patchify_proj.bias"] = rnd(hidden)
+    sd["caption_projection.linear_1.weight"] = rnd(hidden, caption)
+    sd["caption_projection.linear_1.bias"] = rnd(hidden)
+    sd["adaln_single.linear.weight"] = rnd(6 * hidden, hidden)
+    sd["scale_shift_table"] = rnd(2, hidden)
+    sd["proj_out.weight"] = rnd(16, hidden)
+    sd["proj_out.bias"] = rnd(16)
+    return sd
+
+
+def reference_convert_fixture() -> None:
+    """q8_kernels/utils/convert_weights.py:23-78 run on the miniature checkpoint, with its two
+    native calls (Hadamard, quantizer) served by the oracle and ``.cuda()`` made a no-op: pins the
+    key renames, the dtype rules and which tensors get quantised."""
+    _stub("q8_kernels.functional")
+    _stub("q8_kernels.functional.quantizer", quantize=lambda x: O.tokenwise_quant(x))
+    _stub("q8_kernels.functional.fast_hadamard", hadamard_transform=lambda x: O.hadamard_transform(x))
+    _stub("q8_kernels.models")
+    _stub("q8_kernels.models.LTXVideo", get_ltx_transformer=None)
+    ref_conv = _load(os.path.join(REF, "q8_kernels/utils/convert_weights.py"), "ref_convert_weights")
+    sd = synthetic_checkpoint()
+    real_cuda = torch.Tensor.cuda
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    try:
+        out = ref_conv.convert_state_dict(dict(sd))
+    finally:
+        torch.Tensor.cuda = real_cuda
+    arrays = {f"in__{k}": _np(v) for k, v in sd.items()}
+    arrays.update({f"out__{k}": _np(v) for k, v in out.items()})
+    arrays.update({f"dtype__{k}": np.array(str(v.dtype)) for k, v in out.items()})
+    np.savez_compressed(os.path.join(HERE, "ref_convert_state_dict.npz"), **arrays)
+    print("reference convert_state_dict:", len(sd), "->", len(out), "tensors")
+
+
 def oracle_fixtures() -> None:
     E4M3 = torch.float8_e4m3fn
     # quantizer
@@ -140,6 +195,7 @@ def oracle_fixtures() -> None:
 if __name__ == "__main__":
     if os.path.isdir(REF):
         reference_fixtures()
+        reference_convert_fixture()
     else:
         print(f"{REF} not present: reference fixtures left untouched")
     oracle_fixtures()

@@ -183,3 +183,68 @@ def test_dim_checks_raise(nat, cuda_device):
         nat.rope(torch.zeros(2, 64, dtype=torch.bfloat16, device=cuda_device),
                  torch.zeros(2, 64, dtype=torch.bfloat16, device=cuda_device),
                  torch.zeros(2, 64, dtype=torch.bfloat16, device=cuda_device), None)
+
+
+# ---------------------------------------------------------------- training-side gradients
+@pytest.mark.parametrize("dim", [64, 2048, 8192])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, E4M3])
+def test_gelu_backward_vs_oracle(nat, cuda_device, dim, out_dtype):
+    x = Hp.activations(40, dim, seed=dim + 1, outliers=False)
+    g = Hp.activations(40, dim, seed=dim + 2, outliers=False)
+    ref = O.gelu_backward(x, g, out_dtype)
+    got = nat.gelu_backward(x.to(cuda_device), g.to(cuda_device), out_dtype).cpu()
+    assert got.dtype == out_dtype
+    # tanhf and FMA contraction move the fp32 value by an ulp or two: a few outputs may round the other way
+    assert (Hp.bits(got) != Hp.bits(ref)).float().mean().item() < 0.01
+    assert Hp.rel_fro(got.float(), ref.float()) < 2e-3
+
+
+@pytest.mark.parametrize("dim", [64, 2048])
+@pytest.mark.parametrize("shared", [False, True])
+def test_rope_backward_bit_exact(nat, cuda_device, dim, shared):
+    g = Hp.activations(2 * 24, dim, seed=dim + 5).view(2, 24, dim)
+    ang = torch.rand(1 if shared else 2, 24, dim, generator=Hp.gen(7)) * 6.28
+    cos, sin = ang.cos(), ang.sin()
+    ref = O.rope_backward(g, cos.expand(2, 24, dim), sin.expand(2, 24, dim), torch.bfloat16)
+    got = nat.rope_backward(g.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device), torch.bfloat16).cpu()
+    Hp.assert_bit_equal(got, ref, "rope_backward")
+
+
+@pytest.mark.parametrize("dim", [256, 2048, 8192])
+@pytest.mark.parametrize("affine", [False, True])
+def test_rms_norm_backward_vs_oracle(nat, cuda_device, dim, affine):
+    x = Hp.activations(24, dim, seed=dim + 9)
+    w = (0.5 + torch.rand(dim, generator=Hp.gen(3))) if affine else None
+    g = Hp.activations(24, dim, seed=dim + 10, outliers=False)
+    xd = x.to(cuda_device)
+    wd = w.to(cuda_device) if affine else None
+    y, r = nat.rms_norm(xd, wd, torch.bfloat16)
+    ref = O.rms_norm_backward(y.cpu(), r.cpu(), g, w, torch.bfloat16)
+    got = nat.rms_norm_backward(y, r, g.to(cuda_device), wd, torch.bfloat16).cpu()
+    assert (Hp.bits(got) != Hp.bits(ref)).float().mean().item() < 0.01
+    assert Hp.rel_fro(got.float(), ref.float()) < 2e-3
+
+
+def test_autograd_rules_use_the_backward_kernels(nat, cuda_device):
+    import q8_kernels_b200.functional as Q8F
+    dim = 2048
+    x = Hp.activations(16, dim, seed=77, outliers=False).to(cuda_device).requires_grad_(True)
+    w = (0.5 + torch.rand(dim, generator=Hp.gen(4))).to(cuda_device)
+    g = Hp.activations(16, dim, seed=78, outliers=False).to(cuda_device)
+    y = Q8F.rms_norm.rms_norm_8bit(x, w, torch.bfloat16)
+    y.backward(g)
+    # against torch autograd of the same function in fp32
+    xf = x.detach().float().requires_grad_(True)
+    yf = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True)) * w
+    yf.backward(g.float())
+    assert Hp.rel_fro(x.grad.float(), xf.grad) < 1e-2          # bf16 output and bf16 saved activations
+    x2 = Hp.activations(16, dim, seed=79, outliers=False).view(1, 16, dim).to(cuda_device).requires_grad_(True)
+    ang = torch.rand(1, 16, dim, generator=Hp.gen(8)) * 6.28
+    cos, sin = ang.cos().to(cuda_device), ang.sin().to(cuda_device)
+    o = Q8F.rope.apply_rope(x2, cos, sin, torch.bfloat16)
+    o.backward(g.view(1, 16, dim))
+    x2f = x2.detach().float().requires_grad_(True)
+    t = x2f.reshape(1, 16, dim // 2, 2)
+    rot = torch.stack((-t[..., 1], t[..., 0]), dim=-1).reshape(1, 16, dim)
+    (x2f * cos + rot * sin).backward(g.view(1, 16, dim).float())
+    assert Hp.rel_fro(x2.grad.float(), x2f.grad) < 5e-3
