@@ -397,6 +397,44 @@ def bench_detail(q8, dev, peaks, steps):
     return out
 
 
+def bench_head_sharded_block(q8, dev, rank, world):
+    """One DiT block on 6144 tokens with the self- and cross-attention cores sharded by head over the
+    ranks (H / world heads each, NCCL all-gather of the channel slices before the output projection);
+    linears, norms and RoPE replicated.  Max over ranks of the CUDA-event time."""
+    import torch.distributed as dist
+    from q8_kernels_b200 import sharding
+    cfg = q8.blocks.LTXStackConfig(num_layers=1)
+    stack = q8.blocks.random_init_(q8.blocks.LTXStack(cfg), seed=11, device=dev)        # same seed: replicated weights
+    blk = stack.transformer_blocks[0]
+    g = torch.Generator(device="cpu").manual_seed(99)
+    S, T = 6144, 128
+    x = torch.randn(1, S, cfg.inner_dim, generator=g).to(torch.bfloat16).to(dev)
+    text = torch.randn(1, T, cfg.inner_dim, generator=g).to(torch.bfloat16).to(dev)
+    ts = (torch.randn(1, 1, 6 * cfg.inner_dim, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+    freqs = stack.freqs_cis(q8.blocks.latent_grid(16, 16, 24, device=dev))
+    lens = torch.tensor([97], dtype=torch.int32, device=dev)
+    hs = sharding.head_shard(cfg.num_attention_heads, rank, world)
+
+    def run(sharded):
+        with torch.no_grad():
+            if sharded:
+                return blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels", head_shard=hs,
+                           gather_heads=sharding.gather_heads)
+            return blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels")
+
+    same = bool(torch.equal(run(True), run(False)))
+    out = {}
+    for name, sharded in (("replicated_ms", False), ("head_sharded_ms", True)):
+        ms, _ = time_region(lambda: run(sharded) is None or 1, 20, 3, dist.barrier)
+        t = torch.tensor([ms / 20], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name] = round(float(t[0]), 4)
+    out.update({"world": world, "heads_per_rank": cfg.num_attention_heads // world, "tokens": S,
+                "bit_identical_to_replicated": same,
+                "collective": "all_gather_into_tensor of e4m3 [1,6144,2048/world] per attention (NCCL)"})
+    return out
+
+
 # ----------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
@@ -517,6 +555,11 @@ def main():
             line["cpu_baseline"]["value"] = round(cb["value"], 4)
         if args.full:
             line["detail"] = bench_detail(q8, dev, peaks, args.steps)
+    if args.full and world > 1:
+        sharded = bench_head_sharded_block(q8, dev, rank, world)     # collective inside: every rank runs it
+        if rank == 0:
+            line["detail"]["dit_block_head_sharded"] = sharded
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -107,7 +107,7 @@ class Attention(nn.Module):
         # bits: every output column only sees its own weight row), and q/k norm + RoPE + per-head
         # Hadamard + e4m3 cast are one kernel writing the attention kernel's operand layout (same
         # roundings as the op-by-op path below).
-        if (attn_type == "q8_kernels" and self.qk_rms_norm and self.head_dim == 64 and head_shard is None
+        if (attn_type == "q8_kernels" and self.qk_rms_norm and self.head_dim == 64
                 and apply_qk_hadamard and mm_out_dtype == torch.bfloat16 and non_mm_precision == torch.bfloat16
                 and hq.dim() == 3 and (not rope_here or freqs_cis[0].shape[0] == 1)):
             scale = math.sqrt(1 / 64) * math.sqrt(64 ** -0.5)
@@ -127,8 +127,19 @@ class Attention(nn.Module):
                 k8_ = native.qk_norm_rope_prep(kv[..., :C], self.k_norm.weight, None, heads, True, scale)
                 value = kv[..., C:]
             vt8 = native.attention_prep_v(value.unflatten(-1, (heads, self.head_dim)).transpose(1, 2))
+            if head_shard is not None:
+                # projections, q/k norm (it spans all heads) and RoPE ran replicated; the attention core
+                # takes this rank's heads and the channel slices are gathered before the output projection
+                if gather_heads is None:
+                    raise ValueError("head_shard needs a gather_heads callable that reassembles the channel dim")
+                rank, world = head_shard
+                heads = heads // world
+                sl = slice(rank * heads, (rank + 1) * heads)
+                q8_, k8_, vt8 = q8_[:, sl].contiguous(), k8_[:, sl].contiguous(), vt8[:, sl].contiguous()
             hidden_states = native.flash_attention(q8_, k8_, vt8, 1.0, attention_mask, None, token_major_out=True)
             hidden_states = hidden_states.transpose(1, 2).reshape(batch_size, -1, heads * self.head_dim)
+            if head_shard is not None:
+                hidden_states = gather_heads(hidden_states)
             return self._project_out(hidden_states, non_mm_precision, mm_out_dtype, out_gate, out_residual)
 
         query = self.to_q(hq, hs, out_dtype=mm_out_dtype)

@@ -264,3 +264,26 @@ def test_block_is_cuda_graph_capturable(q8, cuda_device):
         torch.cuda.synchronize(d)
     assert torch.equal(captured, want)
     assert not torch.equal(captured, eager)
+
+
+@pytest.mark.parametrize("in_f,out_f", [(4096, 10240), (10240, 4096)])
+@pytest.mark.parametrize("use_hadamard", [False, True])
+def test_fp8_linear_from_linear_at_t5_encoder_dims(cuda_device, in_f, out_f, use_hadamard):
+    """The reference builds its FP8 T5 encoder from FP8Linear.from_linear on 4096 <-> 10240 projections
+    (q8_kernels/models/T5EncoderFP8.py:275-299): 10240 is not a power of two, so the Hadamard variant pads
+    to 16384 and the GEMM runs with K = 10240."""
+    import q8_kernels_b200 as q8
+    lin = torch.nn.Linear(in_f, out_f, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(Hp.weights(out_f, in_f, seed=in_f % 97).float())
+    lin = lin.to(torch.bfloat16)
+    mod = q8.modules.FP8Linear.from_linear(lin, use_hadamard=use_hadamard)
+    wsrc = O.hadamard_transform(lin.weight.data) if use_hadamard else lin.weight.data
+    wq, sw = O.tokenwise_quant(wsrc, E4M3)
+    Hp.assert_bit_equal(mod.weight.data, wq, "weight")
+    Hp.assert_bit_equal(mod.scales.data, sw, "scales")
+    x = Hp.activations(48, in_f, seed=5).reshape(1, 48, in_f)
+    y = mod(x.to(cuda_device))
+    ref = O.fp8_linear(x, wq, None, None, sw, use_hadamard, torch.bfloat16)
+    assert y.shape == (1, 48, out_f) and y.dtype == torch.bfloat16
+    assert Hp.rel_fro(y.float(), ref.float()) <= TOL
