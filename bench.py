@@ -415,23 +415,32 @@ def bench_head_sharded_block(q8, dev, rank, world):
     lens = torch.tensor([97], dtype=torch.int32, device=dev)
     hs = sharding.head_shard(cfg.num_attention_heads, rank, world)
 
+    peers = sharding.PeerBuffers(S * cfg.inner_dim, dev)
+
     def run(sharded):
         with torch.no_grad():
-            if sharded:
+            if sharded == "nccl":
                 return blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels", head_shard=hs,
                            gather_heads=sharding.gather_heads)
+            if sharded == "peer":
+                return blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels", head_shard=hs, peer_buffers=peers)
             return blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels")
 
-    same = bool(torch.equal(run(True), run(False)))
+    ref = run(None)
+    same = bool(torch.equal(run("nccl"), ref)) and bool(torch.equal(run("peer"), ref)) and bool(torch.equal(run("peer"), ref))
     out = {}
-    for name, sharded in (("replicated_ms", False), ("head_sharded_ms", True)):
+    for name, sharded in (("replicated_ms", None), ("head_sharded_nccl_gather_ms", "nccl"),
+                          ("head_sharded_peer_store_ms", "peer")):
         ms, _ = time_region(lambda: run(sharded) is None or 1, 20, 3, dist.barrier)
         t = torch.tensor([ms / 20], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         out[name] = round(float(t[0]), 4)
+    peers.close()
     out.update({"world": world, "heads_per_rank": cfg.num_attention_heads // world, "tokens": S,
                 "bit_identical_to_replicated": same,
-                "collective": "all_gather_into_tensor of e4m3 [1,6144,2048/world] per attention (NCCL)"})
+                "nccl_gather": "all_gather_into_tensor of e4m3 [1,6144,2048/world] per self-attention",
+                "peer_store": "the attention kernel stores its heads into every rank's buffer over NVLink "
+                              "(CUDA IPC mappings); a one-element all-reduce is the only collective"})
     return out
 
 

@@ -175,6 +175,26 @@ Q8K_API int q8k_flash_attention_strided(const void* q, const void* k, const void
                                 int64_t out_stride_s, float softmax_scale, const int* key_lens,
                                 int* dev_status, void* stream);
 
+/* q8k_flash_attention_strided with n_out (1..8) destinations: the finished output tile is stored, with the
+ * same strides, at outs[0..n_out-1].  Destinations may be buffers of other GPUs mapped into this process
+ * (q8k_ipc_open below): with attention sharded by head every rank then writes its heads straight into every
+ * rank's full [B,S,H,64] buffer over NVLink and no all-gather is needed afterwards, only a barrier.  Stores
+ * only: the kernel reads nothing from a peer and waits on none.  No reference counterpart (the reference is
+ * single-GPU).                                                                                          */
+Q8K_API int q8k_flash_attention_multi_out(const void* q, const void* k, const void* vt, void* const* outs, int n_out,
+                                  int out_dtype, int B, int H, int M, int N, int64_t out_stride_b,
+                                  int64_t out_stride_h, int64_t out_stride_s, float softmax_scale,
+                                  const int* key_lens, int* dev_status, void* stream);
+
+/* Set-up helpers for peer destinations (host side, no kernel): export the CUDA IPC handle of the device
+ * allocation that contains ptr plus ptr's offset in it; map such an allocation of another process into this
+ * one with the calling thread's current device (peer access is enabled by the mapping) and return the
+ * address of the same offset; unmap it again.                                                            */
+#define Q8K_IPC_HANDLE_BYTES 64
+Q8K_API int q8k_ipc_export(const void* ptr, unsigned char handle[Q8K_IPC_HANDLE_BYTES], int64_t* offset);
+Q8K_API int q8k_ipc_open(const unsigned char handle[Q8K_IPC_HANDLE_BYTES], int64_t offset, void** ptr);
+Q8K_API int q8k_ipc_close(void* ptr, int64_t offset);
+
 /* Pre-pass of the attention call: from bf16 q,k,v given as strided [B,S,H,64]
  * views (strides in elements, last dim contiguous) produce q8,k8 [B,H,S,64]
  * e4m3 (Hadamard-rotated times qk_scale when apply_hadamard, else plain cast)

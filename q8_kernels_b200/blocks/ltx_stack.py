@@ -81,7 +81,7 @@ class LTXStack(nn.Module):
                                     c.positional_embedding_max_pos)
 
     def forward(self, hidden_states, indices_grid, encoder_hidden_states, encoder_attention_mask, timestep,
-                attn_type="q8_kernels", head_shard=None, gather_heads=None):
+                attn_type="q8_kernels", head_shard=None, gather_heads=None, peer_buffers=None):
         """hidden_states [B,S,inner] bf16; indices_grid [1 or B,3,S]; encoder_hidden_states
         [B,T,caption_channels] bf16; encoder_attention_mask int32 [B] (valid text tokens) or None;
         timestep [B,1,6*inner] modulation values fed to every block."""
@@ -89,7 +89,8 @@ class LTXStack(nn.Module):
         text = self.caption_projection(encoder_hidden_states)
         for block in self.transformer_blocks:
             hidden_states = block(hidden_states, freqs, None, text, encoder_attention_mask, timestep,
-                                  attn_type=attn_type, head_shard=head_shard, gather_heads=gather_heads)
+                                  attn_type=attn_type, head_shard=head_shard, gather_heads=gather_heads,
+                                  peer_buffers=peer_buffers)
         return hidden_states
 
 

@@ -30,7 +30,7 @@ class LTXTransformerBlock(nn.Module):
 
     def forward(self, hidden_states, freqs_cis, attention_mask, encoder_hidden_states, encoder_attention_mask,
                 timestep, mm_out_dtype=torch.bfloat16, non_mm_precision=torch.bfloat16, attn_type="torch",
-                head_shard=None, gather_heads=None, fuse=True):
+                head_shard=None, gather_heads=None, fuse=True, peer_buffers=None):
         num_ada_params = self.scale_shift_table.shape[0]
         ada_values = self.scale_shift_table[None, None] + timestep.reshape(
             hidden_states.shape[0], timestep.shape[1], num_ada_params, -1)
@@ -48,7 +48,8 @@ class LTXTransformerBlock(nn.Module):
             nq = native.norm_modulate_quant(hidden_states, scale_msa, shift_msa)
             hidden_states = self.attn1(None, freqs_cis, None, attention_mask, non_mm_precision, mm_out_dtype,
                                        attn_type=attn_type, head_shard=head_shard, gather_heads=gather_heads,
-                                       hidden_states_q=nq, out_gate=gate_msa, out_residual=hidden_states)
+                                       hidden_states_q=nq, out_gate=gate_msa, out_residual=hidden_states,
+                                       peer_buffers=peer_buffers)
             hidden_states = self.attn2(hidden_states, freqs_cis=freqs_cis, encoder_hidden_states=encoder_hidden_states,
                                        attention_mask=encoder_attention_mask, non_mm_precision=non_mm_precision,
                                        mm_out_dtype=mm_out_dtype, attn_type=attn_type, out_residual=hidden_states)

@@ -66,8 +66,11 @@ struct AttnSmem {
     static constexpr int kDynamic = kTotal + 1024;
 };
 
+constexpr int kAttnMaxOut = 8;           // destinations of the output tile: this GPU's buffer and up to 7 peers'
+
 struct AttnParams {
-    void* out;
+    void* outs[kAttnMaxOut];               // same layout and strides in every destination
+    int n_out;
     const int* key_lens;
     int* status;
     int B, H, M, N;
@@ -469,8 +472,11 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     for (int j = 0; j < 32; ++j) orow[j] = 0u;
                 }
                 if (row < p.M) {
+                  // every destination gets the tile: plain stores, to this GPU's memory or over NVLink to a
+                  // peer's (nothing is read from a peer and nothing here waits on one)
+                  for (int dst = 0; dst < p.n_out; ++dst) {
                     if (p.out_e4m3) {
-                        uint8_t* o = reinterpret_cast<uint8_t*>(p.out) + out_off + h * 32;
+                        uint8_t* o = reinterpret_cast<uint8_t*>(p.outs[dst]) + out_off + h * 32;
 #pragma unroll
                         for (int v4 = 0; v4 < 2; ++v4) {
                             uint32_t w[4];
@@ -483,7 +489,7 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                             reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     } else {
-                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + out_off + h * 32;
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.outs[dst]) + out_off + h * 32;
 #pragma unroll
                         for (int v4 = 0; v4 < 4; ++v4) {
                             uint32_t w[4];
@@ -497,6 +503,7 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                             reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     }
+                  }
                 }
             }
         } else if (p.status != nullptr && threadIdx.x == 128) {
@@ -696,7 +703,22 @@ extern "C" int q8k_flash_attention_strided(const void* q, const void* k, const v
                                            int B, int H, int M, int N, int64_t out_stride_b, int64_t out_stride_h,
                                            int64_t out_stride_s, float softmax_scale, const int* key_lens,
                                            int* dev_status, void* stream) {
+    void* outs[1] = {out};
+    return q8k_flash_attention_multi_out(q, k, vt, outs, 1, out_dtype, B, H, M, N, out_stride_b, out_stride_h,
+                                         out_stride_s, softmax_scale, key_lens, dev_status, stream);
+}
+
+extern "C" int q8k_flash_attention_multi_out(const void* q, const void* k, const void* vt, void* const* outs, int n_out,
+                                             int out_dtype, int B, int H, int M, int N, int64_t out_stride_b,
+                                             int64_t out_stride_h, int64_t out_stride_s, float softmax_scale,
+                                             const int* key_lens, int* dev_status, void* stream) {
     const char* op = "flash_attention";
+    Q8K_REQUIRE(outs != nullptr && n_out >= 1 && n_out <= kAttnMaxOut, Q8K_ERR_INVALID_ARG,
+                "%s: between 1 and %d output destinations", op, kAttnMaxOut);
+    for (int i = 0; i < n_out; ++i)
+        Q8K_REQUIRE(outs[i] != nullptr && aligned16(outs[i]), Q8K_ERR_INVALID_ARG,
+                    "%s: output destination %d is null or not 16-byte aligned", op, i);
+    void* out = outs[0];
     Q8K_REQUIRE(q && k && vt && out, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
     Q8K_REQUIRE(B > 0 && H > 0 && M >= 0 && N > 0, Q8K_ERR_INVALID_ARG, "%s: bad shape B=%d H=%d M=%d N=%d", op, B, H, M, N);
     Q8K_REQUIRE(aligned16(q) && aligned16(k) && aligned16(vt) && aligned16(out), Q8K_ERR_INVALID_ARG,
@@ -731,7 +753,8 @@ extern "C" int q8k_flash_attention_strided(const void* q, const void* k, const v
     }
 
     AttnParams p;
-    p.out = out;
+    for (int i = 0; i < kAttnMaxOut; ++i) p.outs[i] = i < n_out ? outs[i] : nullptr;
+    p.n_out = n_out;
     p.key_lens = key_lens;
     p.status = dev_status;
     p.B = B; p.H = H; p.M = M; p.N = N;

@@ -8,6 +8,8 @@
 
 #include <mutex>
 
+#include <cuda.h>
+#include <string.h>
 #include "common.cuh"
 
 namespace q8k {
@@ -136,4 +138,46 @@ extern "C" int q8k_linear_static(const void* x, int x_dtype, const void* w, int 
     if (w_dtype == Q8K_DT_I8)
         return q8k_q8_mm(xq, w, bias, x_scales, w_scales, out, out_dtype, 1, 1, M, N, K, fuse_gelu, dev_status, stream);
     return q8k_fp8_mm(xq, w, bias, x_scales, w_scales, out, out_dtype, 1, 1, M, N, K, fuse_gelu, dev_status, stream);
+}
+
+// ------------------------------------------------------------------ peer buffers (multi-GPU set-up)
+extern "C" int q8k_ipc_export(const void* ptr, unsigned char handle[Q8K_IPC_HANDLE_BYTES], int64_t* offset) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == Q8K_IPC_HANDLE_BYTES, "IPC handle size");
+    Q8K_REQUIRE(ptr && handle && offset, Q8K_ERR_INVALID_ARG, "ipc_export: null pointer");
+    // the handle names a whole allocation: find its base
+    using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static RangeFn range = []() -> RangeFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<RangeFn>(p);
+    }();
+    Q8K_REQUIRE(range != nullptr, Q8K_ERR_CUDA, "ipc_export: cuMemGetAddressRange is not available");
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    const CUresult r = range(&base, &size, (CUdeviceptr)(uintptr_t)ptr);
+    Q8K_REQUIRE(r == CUDA_SUCCESS, Q8K_ERR_CUDA, "ipc_export: cuMemGetAddressRange failed with CUresult %d", (int)r);
+    cudaIpcMemHandle_t h;
+    Q8K_CUDA_OK(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>((uintptr_t)base)));
+    memcpy(handle, &h, sizeof(h));
+    *offset = (int64_t)((uintptr_t)ptr - (uintptr_t)base);
+    return Q8K_OK;
+}
+
+extern "C" int q8k_ipc_open(const unsigned char handle[Q8K_IPC_HANDLE_BYTES], int64_t offset, void** ptr) {
+    Q8K_REQUIRE(handle && ptr && offset >= 0, Q8K_ERR_INVALID_ARG, "ipc_open: bad argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* base = nullptr;
+    Q8K_CUDA_OK(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr = reinterpret_cast<unsigned char*>(base) + offset;
+    return Q8K_OK;
+}
+
+extern "C" int q8k_ipc_close(void* ptr, int64_t offset) {
+    Q8K_REQUIRE(ptr && offset >= 0, Q8K_ERR_INVALID_ARG, "ipc_close: bad argument");
+    Q8K_CUDA_OK(cudaIpcCloseMemHandle(reinterpret_cast<unsigned char*>(ptr) - offset));
+    return Q8K_OK;
 }

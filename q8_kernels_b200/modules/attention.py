@@ -80,11 +80,13 @@ class Attention(nn.Module):
     def forward(self, hidden_states, freqs_cis=None, encoder_hidden_states=None, attention_mask=None,
                 non_mm_precision=torch.bfloat16, mm_out_dtype=None, apply_qk_hadamard=True, attn_type="torch",
                 head_shard: Optional[Tuple[int, int]] = None, gather_heads=None,
-                hidden_states_q=None, out_gate=None, out_residual=None):
+                hidden_states_q=None, out_gate=None, out_residual=None, peer_buffers=None):
         """Reference signature plus: ``head_shard`` / ``gather_heads`` (attention core on a slice of the
         heads), ``hidden_states_q = (int8, scales)`` when the caller already holds the Hadamard-rotated,
         quantised ``hidden_states`` (the fused norm + modulation producer), and ``out_gate`` /
-        ``out_residual`` to fold ``gate * out + residual`` into the output projection's epilogue."""
+        ``out_residual`` to fold ``gate * out + residual`` into the output projection's epilogue;
+        ``peer_buffers`` (``sharding.PeerBuffers``) instead of ``gather_heads``: the attention kernel stores
+        this rank's heads into every rank's buffer and a barrier replaces the all-gather."""
         if attention_mask is not None and attention_mask.ndim > 1 and attn_type == "q8_kernels":
             attention_mask = attention_mask.argmin(-1).squeeze().int()
             if attention_mask.ndim == 0:
@@ -130,15 +132,25 @@ class Attention(nn.Module):
             if head_shard is not None:
                 # projections, q/k norm (it spans all heads) and RoPE ran replicated; the attention core
                 # takes this rank's heads and the channel slices are gathered before the output projection
-                if gather_heads is None:
-                    raise ValueError("head_shard needs a gather_heads callable that reassembles the channel dim")
+                if gather_heads is None and peer_buffers is None:
+                    raise ValueError("head_shard needs gather_heads or peer_buffers to reassemble the channel dim")
                 rank, world = head_shard
                 heads = heads // world
                 sl = slice(rank * heads, (rank + 1) * heads)
                 q8_, k8_, vt8 = q8_[:, sl].contiguous(), k8_[:, sl].contiguous(), vt8[:, sl].contiguous()
+                if peer_buffers is not None:
+                    seq = q8_.shape[2]
+                    local, addrs = peer_buffers.next(batch_size * seq * self.inner_dim)
+                    native.flash_attention_into(q8_, k8_, vt8, 1.0, attention_mask, torch.float8_e4m3fn, addrs,
+                                                self.num_heads, rank * heads)
+                    peer_buffers.barrier()
+                    hidden_states = local.view(torch.float8_e4m3fn).view(batch_size, seq, self.inner_dim)
+                    return self._project_out(hidden_states, non_mm_precision, mm_out_dtype, out_gate, out_residual)
             hidden_states = native.flash_attention(q8_, k8_, vt8, 1.0, attention_mask, None, token_major_out=True)
             hidden_states = hidden_states.transpose(1, 2).reshape(batch_size, -1, heads * self.head_dim)
             if head_shard is not None:
+                if gather_heads is None:
+                    raise ValueError("head_shard needs a gather_heads callable on this path")
                 hidden_states = gather_heads(hidden_states)
             return self._project_out(hidden_states, non_mm_precision, mm_out_dtype, out_gate, out_residual)
 

@@ -9,7 +9,9 @@ synchronises.
 from __future__ import annotations
 
 import math
-from typing import List, Optional, Tuple
+from typing import Sequence, List, Optional, Tuple
+
+import ctypes
 
 import torch
 
@@ -407,6 +409,41 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_s
                                               float(softmax_scale), ptr(batch_mask), ptr(_lib.status_word(dev)),
                                               stream_ptr(dev)), "flash_attention")
     return buf.transpose(1, 2) if token_major_out else buf
+
+
+def flash_attention_into(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,
+                         batch_mask: Optional[torch.Tensor], out_type: torch.dtype, dest_ptrs: Sequence[int],
+                         total_heads: int, first_head: int) -> None:
+    """Head-sharded attention writing straight into full token-major buffers: q, k, v hold this rank's
+    heads ([B,h,M,64] etc.); every address in ``dest_ptrs`` is the start of a [B,M,total_heads,64] buffer
+    of ``out_type`` (this GPU's, or a peer's mapped with ``q8k_ipc_open``) and receives heads
+    ``first_head .. first_head+h`` of the result.  Returns nothing: the buffers are the result."""
+    dev = require_cuda(q, k, v, batch_mask)
+    if q.dtype != E4M3 or k.dtype != E4M3 or v.dtype != E4M3:
+        raise Q8KernelError("flash_attention: q, k, v must be float8_e4m3fn")
+    B, h, M, D = q.shape
+    N = k.shape[2]
+    n_pad = (N + 15) // 16 * 16
+    if D != 64 or tuple(k.shape) != (B, h, N, 64) or tuple(v.shape) != (B, h, 64, n_pad):
+        raise Q8KernelError("flash_attention: q [B,h,M,64], k [B,h,N,64], v [B,h,64,ceil16(N)] expected")
+    if not (0 <= first_head and first_head + h <= total_heads):
+        raise Q8KernelError("flash_attention: head range outside the destination buffers")
+    if not 1 <= len(dest_ptrs) <= 8:
+        raise Q8KernelError("flash_attention: between 1 and 8 destinations")
+    if batch_mask is not None:
+        if batch_mask.dtype != torch.int32 or batch_mask.dim() != 1 or batch_mask.shape[0] != B:
+            raise Q8KernelError("flash_attention: batch_mask must be int32 [B]")
+        batch_mask = batch_mask.contiguous()
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    esz = 1 if out_type == E4M3 else 2
+    head_off = first_head * 64 * esz
+    outs = (ctypes.c_void_p * len(dest_ptrs))(*[int(a) + head_off for a in dest_ptrs])
+    strides = (M * total_heads * 64, 64, total_heads * 64)
+    with torch.cuda.device(dev):
+        check(lib.q8k_flash_attention_multi_out(ptr(q), ptr(k), ptr(v), ctypes.cast(outs, ctypes.c_void_p), len(dest_ptrs),
+                                                dt(out_type), B, h, M, N, *strides, float(softmax_scale),
+                                                ptr(batch_mask), ptr(_lib.status_word(dev)), stream_ptr(dev)),
+              "flash_attention")
 
 
 def attention_prep(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, apply_hadamard: bool,

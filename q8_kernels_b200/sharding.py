@@ -76,3 +76,76 @@ def gather_videos(x_local: torch.Tensor, counts: List[int], group: Optional[dist
     out = torch.empty((world * most,) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=x_local.device)
     dist.all_gather_into_tensor(out, padded, group=group)
     return torch.cat([out[r * most: r * most + n] for r, n in enumerate(counts)], dim=0)
+
+
+class PeerBuffers:
+    """Gather-free head sharding: a device buffer on every rank that all the other ranks of the node
+    can store into.
+
+    Each rank allocates ``2 * nbytes`` bytes, exports the allocation with CUDA IPC and maps every
+    other rank's into its own process (peer access over NVLink comes with the mapping).  The
+    attention kernel of a rank then stores its heads of the output into the same place of EVERY
+    rank's buffer (``native.flash_attention_into``), and after ``barrier()`` -- a one-element NCCL
+    all-reduce on the current stream, which no rank leaves before all have entered, i.e. before all
+    their attention kernels have finished -- every rank holds the complete output.  The two halves
+    alternate from call to call: a rank that is already writing the next attention output cannot
+    touch the half a slower peer is still reading, because it cannot get two calls ahead without that
+    peer having passed the barrier in between.
+
+    Nothing here reads from a peer, and no kernel waits on a peer: the only cross-rank wait is the
+    NCCL collective, which has the process group's timeout.
+    """
+
+    def __init__(self, nbytes: int, device, group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+        from ._lib import check, lib
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
+        self.device = torch.device(device)
+        self._store = torch.empty(2 * self.nbytes, dtype=torch.uint8, device=self.device)
+        self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._turn = 0
+        self._opened = []
+        handle = (ctypes.c_ubyte * 64)()
+        offset = ctypes.c_int64(0)
+        with torch.cuda.device(self.device):
+            check(lib.q8k_ipc_export(ctypes.c_void_p(self._store.data_ptr()), ctypes.cast(handle, ctypes.c_void_p),
+                                     ctypes.cast(ctypes.pointer(offset), ctypes.c_void_p)), "ipc_export")
+            mine = (bytes(handle), int(offset.value))
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=group)
+            self._base = []
+            for r, (h, off) in enumerate(everyone):
+                if r == self.rank:
+                    self._base.append(self._store.data_ptr())
+                    continue
+                hbuf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                p = ctypes.c_void_p(0)
+                check(lib.q8k_ipc_open(ctypes.cast(hbuf, ctypes.c_void_p), off,
+                                       ctypes.cast(ctypes.pointer(p), ctypes.c_void_p)), "ipc_open")
+                self._opened.append((p.value, off))
+                self._base.append(p.value)
+        dist.barrier(group=group)                               # every mapping exists before anyone stores
+
+    def next(self, nbytes: int) -> Tuple[torch.Tensor, List[int]]:
+        """This call's half: (local uint8 view of ``nbytes`` bytes, its address on every rank, by rank)."""
+        if nbytes > self.nbytes:
+            raise ValueError(f"peer buffers hold {self.nbytes} bytes per call, {nbytes} asked for")
+        half = self._turn * self.nbytes
+        self._turn ^= 1
+        return self._store[half: half + nbytes], [b + half for b in self._base]
+
+    def barrier(self) -> None:
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self) -> None:
+        from ._lib import check, lib
+        import ctypes
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)                          # nobody unmaps while a peer may still store
+        with torch.cuda.device(self.device):
+            for addr, off in self._opened:
+                check(lib.q8k_ipc_close(ctypes.c_void_p(addr), off), "ipc_close")
+        self._opened = []

@@ -46,6 +46,13 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             shard = blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels",
                         head_shard=sharding.head_shard(8, rank, world), gather_heads=sharding.gather_heads)
             ok_heads = torch.equal(full, shard)            # same kernels on the same heads: identical bits
+            # the same with the attention kernel storing its heads straight into every rank's buffer
+            peers = sharding.PeerBuffers(2 * S * 512, dev)
+            for _ in range(3):                             # both halves of the buffers, and reuse
+                direct = blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels",
+                             head_shard=sharding.head_shard(8, rank, world), peer_buffers=peers)
+                ok_heads = ok_heads and torch.equal(full, direct)
+            peers.close()
             # by video: each rank runs its own video, final gather restores the batch
             mine = list(sharding.video_shard(2, rank, world))
             local = blk(x[mine], freqs, None, text[mine], lens[mine], ts[mine], attn_type="q8_kernels")
