@@ -427,8 +427,15 @@ def bench_head_sharded_block(q8, dev, rank, world):
             return blk(x, freqs, None, text, lens, ts, attn_type="q8_kernels")
 
     ref = run(None)
-    same = bool(torch.equal(run("nccl"), ref)) and bool(torch.equal(run("peer"), ref)) and bool(torch.equal(run("peer"), ref))
-    out = {}
+    checks = {}
+    for name in ("replicated_again", "nccl", "peer", "peer_again"):
+        got = run({"replicated_again": None, "peer_again": "peer"}.get(name, name))
+        checks[name] = int((got != ref).sum())
+    t = torch.tensor([checks[k] for k in sorted(checks)], device=dev, dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)                  # worst rank
+    mismatches = dict(zip(sorted(checks), (int(v) for v in t)))
+    same = not any(mismatches.values())
+    out = {"mismatching_elements_vs_replicated_max_over_ranks": mismatches}
     for name, sharded in (("replicated_ms", None), ("head_sharded_nccl_gather_ms", "nccl"),
                           ("head_sharded_peer_store_ms", "peer")):
         ms, _ = time_region(lambda: run(sharded) is None or 1, 20, 3, dist.barrier)

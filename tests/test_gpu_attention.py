@@ -188,3 +188,21 @@ def test_paired_qk_prep_is_two_single_calls(nat, cuda_device):
     q8, k8 = nat.qk_norm_rope_prep_pair(qkv[..., :C], qkv[..., C:2 * C], wq, wk, fc, H, True, scale)
     assert torch.equal(Hp.bits(q8), Hp.bits(nat.qk_norm_rope_prep(qkv[..., :C], wq, fc, H, True, scale)))
     assert torch.equal(Hp.bits(k8), Hp.bits(nat.qk_norm_rope_prep(qkv[..., C:2 * C], wk, fc, H, True, scale)))
+
+
+def test_head_slices_written_into_several_full_buffers(nat, cuda_device):
+    """The multi-destination output used by gather-free head sharding, on one GPU: two "ranks" each own
+    half of the heads and store them into both of two full token-major buffers."""
+    B, H, S = 2, 4, 200
+    q, k, v = (t.to(cuda_device) for t in Hp.qkv(B, H, S, 64, seed=77))
+    scale = math.sqrt(1 / 64) * math.sqrt(64 ** -0.5)
+    q8, k8, vt8 = nat.attention_prep(q, k, v, True, scale)
+    want = nat.flash_attention(q8, k8, vt8, 1.0, None, None, token_major_out=True).transpose(1, 2).contiguous()  # [B,S,H,64]
+    bufs = [torch.zeros(B, S, H, 64, dtype=torch.uint8, device=cuda_device).view(E4M3) for _ in range(2)]
+    for r in range(2):
+        sl = slice(2 * r, 2 * r + 2)
+        nat.flash_attention_into(q8[:, sl], k8[:, sl], vt8[:, sl], 1.0, None, E4M3, [b.data_ptr() for b in bufs], H, 2 * r)
+    for b in bufs:
+        assert torch.equal(Hp.bits(b), Hp.bits(want))
+    with pytest.raises(Exception):
+        nat.flash_attention_into(q8, k8, vt8, 1.0, None, E4M3, [bufs[0].data_ptr()], H, 2)     # heads 2..6 of 4
