@@ -3,8 +3,8 @@
 Two kinds of file:
 
 * ``ref_*.npz`` -- produced by importing the reference's own pure-torch code
-  from a checkout of KONAKONA666/q8_kernels (path in $Q8_REFERENCE, default
-  /root/reference): ``apply_rope`` (q8_kernels/functional/rope.py:25-43, the
+  from a checkout of KONAKONA666/q8_kernels (path in $Q8_REFERENCE):
+  ``apply_rope`` (q8_kernels/functional/rope.py:25-43, the
   path the reference really runs) and ``precompute_freqs_cis``
   (q8_kernels/models/LTXVideo.py:86-148).  Their native and diffusers imports
   are replaced by inert stubs; only torch arithmetic of the reference executes.
@@ -16,7 +16,7 @@ Two kinds of file:
   of the oracle shows up as a diff.  The reference has no tests or vectors for
   these ops, so they are NOT pinned by the reference.
 
-Usage:  python tests/golden/make_golden.py
+Usage:  Q8_REFERENCE=<checkout of the reference> python tests/golden/make_golden.py
 """
 import importlib.util
 import os
@@ -34,7 +34,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 from oracle import q8_oracle as O  # noqa: E402
 import helpers as Hp  # noqa: E402
 
-REF = os.environ.get("Q8_REFERENCE", "/root/reference")
+REF = os.environ.get("Q8_REFERENCE", "")
 
 
 def _np(t: torch.Tensor) -> np.ndarray:
@@ -193,9 +193,9 @@ def oracle_fixtures() -> None:
 
 
 if __name__ == "__main__":
-    if os.path.isdir(REF):
+    if REF and os.path.isdir(REF):
         reference_fixtures()
         reference_convert_fixture()
     else:
-        print(f"{REF} not present: reference fixtures left untouched")
+        print("$Q8_REFERENCE does not name a checkout of the reference: reference fixtures left untouched")
     oracle_fixtures()
