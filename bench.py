@@ -442,6 +442,7 @@ def bench_head_sharded_block(q8, dev, rank, world):
         t = torch.tensor([ms / 20], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         out[name] = round(float(t[0]), 4)
+    q8._lib.check_status(dev)
     peers.close()
     out.update({"world": world, "heads_per_rank": cfg.num_attention_heads // world, "tokens": S,
                 "bit_identical_to_replicated": same,
