@@ -415,7 +415,8 @@ def bench_head_sharded_block(q8, dev, rank, world):
     lens = torch.tensor([97], dtype=torch.int32, device=dev)
     hs = sharding.head_shard(cfg.num_attention_heads, rank, world)
 
-    peers = sharding.PeerBuffers(S * cfg.inner_dim, dev)
+    use_peers = world <= sharding.PeerBuffers.MAX_WORLD
+    peers = sharding.PeerBuffers(S * cfg.inner_dim, dev) if use_peers else None
 
     def run(sharded):
         with torch.no_grad():
@@ -428,7 +429,7 @@ def bench_head_sharded_block(q8, dev, rank, world):
 
     ref = run(None)
     checks = {}
-    for name in ("replicated_again", "nccl", "peer", "peer_again"):
+    for name in ("replicated_again", "nccl") + (("peer", "peer_again") if use_peers else ()):
         got = run({"replicated_again": None, "peer_again": "peer"}.get(name, name))
         checks[name] = int((got != ref).sum())
     t = torch.tensor([checks[k] for k in sorted(checks)], device=dev, dtype=torch.int64)
@@ -436,14 +437,15 @@ def bench_head_sharded_block(q8, dev, rank, world):
     mismatches = dict(zip(sorted(checks), (int(v) for v in t)))
     same = not any(mismatches.values())
     out = {"mismatching_elements_vs_replicated_max_over_ranks": mismatches}
-    for name, sharded in (("replicated_ms", None), ("head_sharded_nccl_gather_ms", "nccl"),
-                          ("head_sharded_peer_store_ms", "peer")):
+    for name, sharded in (("replicated_ms", None), ("head_sharded_nccl_gather_ms", "nccl")) + \
+            ((("head_sharded_peer_store_ms", "peer"),) if use_peers else ()):
         ms, _ = time_region(lambda: run(sharded) is None or 1, 20, 3, dist.barrier)
         t = torch.tensor([ms / 20], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         out[name] = round(float(t[0]), 4)
     q8._lib.check_status(dev)
-    peers.close()
+    if peers is not None:
+        peers.close()
     out.update({"world": world, "heads_per_rank": cfg.num_attention_heads // world, "tokens": S,
                 "bit_identical_to_replicated": same,
                 "nccl_gather": "all_gather_into_tensor of e4m3 [1,6144,2048/world] per self-attention",

@@ -506,6 +506,11 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                   }
                 }
             }
+            // Stores to another GPU are posted: the end of this kernel orders them for work that follows on
+            // THIS GPU, not for a peer that learns of the kernel's end through a collective taking another
+            // route through the switch (an in-switch all-reduce overtook them on 8 GPUs).  A system-scope fence
+            // holds each thread until its stores are visible everywhere, so "kernel finished" implies "landed".
+            if (p.n_out > 1) __threadfence_system();
         } else if (p.status != nullptr && threadIdx.x == 128) {
             atomicExch(p.status, Q8K_STATUS_TIMEOUT | (6 << 8));
         }
