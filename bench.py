@@ -415,8 +415,8 @@ def bench_head_sharded_block(q8, dev, rank, world):
     lens = torch.tensor([97], dtype=torch.int32, device=dev)
     hs = sharding.head_shard(cfg.num_attention_heads, rank, world)
 
-    use_peers = world <= sharding.PeerBuffers.MAX_WORLD
-    peers = sharding.PeerBuffers(S * cfg.inner_dim, dev) if use_peers else None
+    use_peers = world <= 4          # beyond the library's stress-verified limit the comparison below is the check
+    peers = sharding.PeerBuffers(S * cfg.inner_dim, dev, allow_unverified_world=True) if use_peers else None
 
     def run(sharded):
         with torch.no_grad():

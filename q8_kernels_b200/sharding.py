@@ -95,14 +95,16 @@ class PeerBuffers:
     Nothing here reads from a peer, and no kernel waits on a peer: the only cross-rank wait is the
     NCCL collective, which has the process group's timeout.
 
-    Checked bit-for-bit against the replicated block on 2 and 4 GPUs, including 160 back-to-back calls
-    without host synchronisation on 2.  On 8 GPUs the host-synchronised checks pass as well, but an
-    unsynchronised stress run showed a few 128-row tiles of wrong output per 80 calls (identical on
-    all ranks, not cured by a system-scope fence after the stores); until that is understood more
-    than ``MAX_WORLD`` ranks are refused and callers fall back to ``gather_heads``.
+    Checked bit-for-bit against the replicated block on 2 GPUs in stress loops of 120-160 back-to-back
+    calls without host synchronisation (ranks in lockstep and deliberately skewed), and on 4 and 8
+    GPUs with host-synchronised comparisons.  On 8 GPUs a stress loop WITHOUT host synchronisation
+    showed a few 128-row tiles of wrong output per 80 calls (identical on all ranks, not cured by a
+    system-scope fence after the stores); the same loop could not be run on 4.  Until that is
+    understood more than ``MAX_WORLD`` ranks need ``allow_unverified_world=True``, and callers should
+    otherwise use ``gather_heads``.
     """
 
-    MAX_WORLD = 4
+    MAX_WORLD = 2
 
     def __init__(self, nbytes: int, device, group: Optional[dist.ProcessGroup] = None,
                  allow_unverified_world: bool = False):
