@@ -97,9 +97,11 @@ class PeerBuffers:
 
     Checked bit-for-bit against the replicated block on 2 GPUs in stress loops of 120-160 back-to-back
     calls without host synchronisation (ranks in lockstep and deliberately skewed), and on 4 and 8
-    GPUs with host-synchronised comparisons.  On 8 GPUs a stress loop WITHOUT host synchronisation
-    showed a few 128-row tiles of wrong output per 80 calls (identical on all ranks, not cured by a
-    system-scope fence after the stores); the same loop could not be run on 4.  Until that is
+    GPUs with host-synchronised comparisons.  On 8 GPUs stress loops WITHOUT host synchronisation
+    showed, in 0.5 % of the rank-calls, one 128-row tile of the calling rank's own head slice computed
+    differently (1-4 % of its bytes) and stored like that in every rank's buffer; the replicated and
+    NCCL-gather variants never showed it and a system-scope fence after the stores changes nothing,
+    so it is a timing-sensitive fault of the computing rank, not a lost transfer.  Until that is
     understood more than ``MAX_WORLD`` ranks need ``allow_unverified_world=True``, and callers should
     otherwise use ``gather_heads``.
     """
