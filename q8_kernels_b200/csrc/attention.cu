@@ -345,7 +345,11 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             const float m_scaled = m_new == -INFINITY ? 0.f : m_new * c;
             const float alpha = m_run == -INFINITY ? 0.f : fast_exp2((m_run - m_new) * c);
 
-            if (i > 0 && __any_sync(0xffffffffu, m_new != m_run)) {
+            // pv_done is waited on by parity, which only tells phases apart while the waiter is at
+            // most one phase behind.  So every step observes phase i-1 exactly once: here when O
+            // has to be rescaled, otherwise after the exps (where it has long completed).
+            const bool rescale = i > 0 && __any_sync(0xffffffffu, m_new != m_run);
+            if (rescale) {
                 // O is complete once P.V of the previous block has retired
                 ok = ptx::mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
@@ -441,6 +445,12 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
             }
             if (!ok) break;
+            if (i > 0 && !rescale) {
+                // keep in step with pv_done (see above); P.V of block i-1 retired during the exps
+                ok = ptx::mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
             l_run = l_run * alpha + row_sum;
             m_run = m_new;
             ptx::fence_proxy_async_smem();                     // P visible to the tensor core's smem reads
@@ -452,7 +462,8 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             }
         }
 
-        // epilogue: O / l
+        // epilogue: O / l.  The loop has observed pv_done through phase nblk-2, so the parity of
+        // phase nblk-1 is unambiguous here.
         if (ok && nblk > 0) ok = ptx::mbar_wait(pv_done, (uint32_t)(nblk - 1) & 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {

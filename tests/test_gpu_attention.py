@@ -206,3 +206,77 @@ def test_head_slices_written_into_several_full_buffers(nat, cuda_device):
         assert torch.equal(Hp.bits(b), Hp.bits(want))
     with pytest.raises(Exception):
         nat.flash_attention_into(q8, k8, vt8, 1.0, None, E4M3, [bufs[0].data_ptr()], H, 2)     # heads 2..6 of 4
+
+
+@pytest.mark.parametrize("N", [128, 6144])
+def test_all_equal_keys_never_move_the_row_max(nat, cuda_device, N):
+    """Every key identical: the row max is set by the first block visited and never moves again, so
+    no step rescales O and the kernel's only reason to look at the P.V completion barrier inside
+    the loop is to stay in step with it.  2 blocks (cross-attention size) and 96 blocks."""
+    B, H, M = 1, 2, 256
+    q8, k8, vt, ks = _fp8_operands(B, H, M, N, seed=5)
+    k8 = k8[:, :, :1].expand(B, H, N, 64).contiguous()
+    ref = O.flash_attention(q8, k8, vt, ks, None, torch.bfloat16)
+    d = cuda_device
+    for _ in range(20):
+        got = nat.flash_attention(q8.to(d), k8.to(d), vt.to(d), ks, None, torch.bfloat16)
+        err = Hp.rel_fro(got.float(), ref.float())
+        assert err <= TOL, f"rel fro {err:.3e}"
+
+
+def test_bit_stable_under_memory_pressure(nat, cuda_device):
+    """The config-3 head slice (S = 6144) launched 320 times while a second stream keeps HBM busy
+    with large copies: a V tile that lands late must not change a single output byte."""
+    B, H, S = 1, 8, 6144
+    d = cuda_device
+    q8, k8, vt, ks = (t.to(d) if isinstance(t, torch.Tensor) else t for t in _fp8_operands(B, H, S, S, seed=31))
+    want = nat.flash_attention(q8, k8, vt, ks, None, torch.bfloat16)
+    torch.cuda.synchronize()
+    src = torch.empty(1 << 30, dtype=torch.uint8, device=d)
+    dst = torch.empty_like(src)
+    side = torch.cuda.Stream(device=d)
+    outs = []
+    bad = 0
+    for it in range(320):
+        if it % 4 == 0:
+            with torch.cuda.stream(side):
+                dst.copy_(src, non_blocking=True)
+        outs.append(nat.flash_attention(q8, k8, vt, ks, None, torch.bfloat16))
+        if len(outs) == 16:
+            torch.cuda.synchronize()
+            bad += sum(0 if torch.equal(o, want) else 1 for o in outs)
+            outs.clear()
+    torch.cuda.synchronize()
+    bad += sum(0 if torch.equal(o, want) else 1 for o in outs)
+    assert bad == 0, f"{bad} of 320 launches differ from the first"
+
+
+def test_cross_attention_full_shape_sampled(nat, cuda_device):
+    """Q [2,32,6144,64] x K/V [2,32,128,64] with key-padding lengths drawn from 16..128: sampled
+    (batch, head, row) triples against the oracle."""
+    B, H, M, N = 2, 32, 6144, 128
+    q8, k8, vt, ks = _fp8_operands(B, H, M, N, seed=404)
+    lens = torch.randint(16, 129, (B,), generator=Hp.gen(404), dtype=torch.int32)
+    d = cuda_device
+    got = nat.flash_attention(q8.to(d), k8.to(d), vt.to(d), ks, lens.to(d), torch.bfloat16).cpu()
+    heads = [0, 13, 31]
+    rows = torch.randperm(M, generator=Hp.gen(7))[:192].sort().values
+    ref = O.flash_attention(q8[:, heads][:, :, rows].contiguous(), k8[:, heads].contiguous(),
+                            vt[:, heads].contiguous(), ks, lens, torch.bfloat16)
+    err = Hp.rel_fro(got[:, heads][:, :, rows].float(), ref.float())
+    assert err <= TOL, f"rel fro {err:.3e}"
+
+
+def test_self_attention_full_shape_sampled(nat, cuda_device):
+    """B = 2, H = 32, S = 6144 (the whole self-attention of one DiT block for two videos): sampled
+    (head, row) pairs of both batch entries against the oracle."""
+    B, H, S = 2, 32, 6144
+    q8, k8, vt, ks = _fp8_operands(B, H, S, S, seed=303)
+    d = cuda_device
+    got = nat.flash_attention(q8.to(d), k8.to(d), vt.to(d), ks, None, torch.bfloat16).cpu()
+    heads = [3, 30]
+    rows = torch.randperm(S, generator=Hp.gen(8))[:64].sort().values
+    ref = O.flash_attention(q8[:, heads][:, :, rows].contiguous(), k8[:, heads].contiguous(),
+                            vt[:, heads].contiguous(), ks, None, torch.bfloat16)
+    err = Hp.rel_fro(got[:, heads][:, :, rows].float(), ref.float())
+    assert err <= TOL, f"rel fro {err:.3e}"
