@@ -52,6 +52,10 @@ extern "C" {
 #define Q8K_STATUS_TIMEOUT  0x1
 
 Q8K_API int         q8k_version(void);
+/* Self-test of the bounded wait: one warp waits on a barrier that nothing signals, gives up after
+ * `tries` (1..65536) tests and records  Q8K_STATUS_TIMEOUT | (9 << 8)  in *dev_status.  The kernel
+ * returns normally and the context stays usable.  No counterpart in the reference.              */
+Q8K_API int         q8k_wait_selftest(int* dev_status, unsigned tries, void* stream);
 Q8K_API const char* q8k_error_string(int code);
 Q8K_API const char* q8k_last_error_detail(void);
 

@@ -32,6 +32,7 @@ SIGNATURES = {
     "q8k_version": (_c_int, []),
     "q8k_error_string": (ctypes.c_char_p, [_c_int]),
     "q8k_last_error_detail": (ctypes.c_char_p, []),
+    "q8k_wait_selftest": (_c_int, [_c_ptr, ctypes.c_uint, _c_ptr]),
     "q8k_tokenwise_quant": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_i64, _c_ptr]),
     "q8k_fast_hadamard_transform": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_i64, _c_int, _c_i64, _c_f32, _c_ptr]),
     "q8k_hadamard_quant": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_i64, _c_int, _c_i64, _c_f32, _c_ptr]),

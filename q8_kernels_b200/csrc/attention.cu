@@ -15,22 +15,25 @@
 // and the result is the mean of V, as in the reference.
 //
 // Structure: one CTA per 128 query rows of one (batch, head), two warpgroups
-// whose register budgets are rebalanced with setmaxnreg (24 / 104 per thread).
+// whose register budgets are rebalanced with setmaxnreg (24 / 136 per thread),
+// three CTAs per SM (registers; 3 x 128 TMEM columns).
 //   warp 0      TMA: Q tile once, then K (64 keys x 64 B) and V^T (64 x 64 keys)
-//               tiles, all 64B-swizzled, through KS-deep mbarrier rings
+//               tiles, all 64B-swizzled, into rings of three; one wait per block
 //   warp 1      TMEM allocation; one thread issues S = Q.K^T (2 x tcgen05.mma
 //               M128 N64 K32) into TMEM columns [0,64) and O += P.V (2 x M128 N64
-//               K32) into columns [64,128)
+//               K32) into columns [64,128); one blocking wait per block
 //   warps 4-7   softmax, one thread per query row: the scores of block i sit in
 //               registers (each half is refilled from TMEM with block i+1 as soon
-//               as its exps are done, which also frees S for the next Q.K^T), max,
-//               O *= alpha in TMEM when a row max of the warp moved, exp2, P as
-//               e4m3 into one of two swizzled shared tiles (the A operand of
-//               P.V); at the end O / l -> bf16 or e4m3 -> global
-// The softmax chain of one CTA is latency bound (barrier hand-offs, TMEM round
-// trips), so the kernel is sized for FOUR resident CTAs per SM -- 128 TMEM
-// columns, 64 registers per thread at launch, ~50 KB shared memory -- and lets
-// the warp schedulers interleave them to keep the exp2 unit busy.
+//               as its exps are done), max, exp2, P as e4m3 into one of two
+//               swizzled shared tiles (the A operand of P.V), then -- only when a
+//               row max of the warp moved -- O *= alpha in TMEM through the
+//               registers of the finished half; at the end O / l -> global
+// Three mbarriers carry the steady state: step_end (softmax -> MMA: P written, O
+// rescaled, S read), s_full (MMA -> softmax: next scores landed AND the previous
+// P.V retired) and slot_free (MMA -> TMA).  Every wait is on consecutive phases
+// of its barrier, so a parity is never ambiguous, and every wait is bounded.
+
+#include <type_traits>
 
 #include "common.cuh"
 #include "tcgen05.cuh"
@@ -43,9 +46,9 @@ constexpr int kAttnBM = 128;
 constexpr int kAttnBN = 64;
 constexpr int kAttnKS = 3;                   // K and V ring depth
 constexpr int kAttnThreads = 256;            // warpgroup 0: TMA + MMA, warpgroup 1: softmax
-constexpr int kAttnRegsLaunch = 64;          // registers per thread at launch: 4 CTAs x 256 threads x 64 = 65536
+constexpr int kAttnRegsLaunch = 80;          // registers per thread at launch: 3 CTAs x 256 threads x 80 = 61440
 constexpr int kAttnRegsIo = 24;              // after setmaxnreg: TMA / MMA warpgroup
-constexpr int kAttnRegsSoftmax = 104;        //                    softmax warpgroup (2 * 64 = 24 + 104)
+constexpr int kAttnRegsSoftmax = 136;        //                    softmax warpgroup (2 * 80 = 24 + 136)
 constexpr int kAttnTmemCols = 128;           // S: [0,64), O: [64,128)
 constexpr uint32_t kAttnOCol = kAttnBN;
 
@@ -59,7 +62,8 @@ struct AttnSmem {
     static constexpr int kVOff = kKOff + kAttnKS * kKBytes;
     static constexpr int kPOff = kVOff + kAttnKS * kVBytes;
     static constexpr int kBarOff = kPOff + 2 * kPBytes;
-    static constexpr int kNumBars = 1 + 4 * kAttnKS + 5;
+    // q_full, k_full[3], v_full[3], slot_free, s_full, step_end
+    static constexpr int kNumBars = 1 + 2 * kAttnKS + 3;
     static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemPtrOff + 4;
     static constexpr int kTotal = kAbortOff + 4;
@@ -90,18 +94,11 @@ template <int N> __device__ __forceinline__ void reg_dealloc() {
 template <int N> __device__ __forceinline__ void reg_alloc() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
-// One arrival per warp: every lane has done its own fences, the warp converges, lane 0 signals.
-__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(bar);
-}
-// sm_100 packed fp32 pairs (one issue slot for two lanes of FMA-pipe work) and 3-input max
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-// four fp32 -> four e4m3 (saturating) packed in one word, lowest byte first
 __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
     uint32_t r;
     asm("{\n\t"
@@ -114,10 +111,20 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
         : "f"(a), "f"(b), "f"(c), "f"(d));
     return r;
 }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// All waits of this kernel: see ptx::mbar_wait_bounded.  A wait that gave up returns like one
+// that succeeded, so no control flow hangs off its result: the kernel runs to its end on garbage
+// and reports the abort word through the status word.
+__device__ __forceinline__ void bounded_wait(uint32_t bar, uint32_t parity, uint32_t abort_addr, uint32_t site) {
+    ptx::mbar_wait_bounded(bar, parity, abort_addr, site, ptx::kSpinLimit);
+}
 
 __global__ void __maxnreg__(kAttnRegsLaunch)
 flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                      const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+               const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
     using L = AttnSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -125,22 +132,18 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const uint32_t bar_base = smem_base + L::kBarOff;
     const uint32_t q_full = bar_base;
     auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
-    auto k_empty = [&](int s) { return bar_base + 8u * (1 + kAttnKS + s); };
-    auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * kAttnKS + s); };
-    auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * kAttnKS + s); };
-    const uint32_t misc = bar_base + 8u * (1 + 4 * kAttnKS);
-    const uint32_t s_full = misc;                                // Q.K^T of block i landed in S        (phase i)
-    const uint32_t s_free = misc + 8u;                           // softmax holds block i in registers  (phase i)
-    auto p_full = [&](int b) { return misc + 8u * (2 + b); };    // softmax wrote P[b], O is rescaled   (phase i/2)
-    const uint32_t pv_done = misc + 32u;                         // P.V of block i retired              (phase i)
+    auto v_full = [&](int s) { return bar_base + 8u * (1 + kAttnKS + s); };
+    const uint32_t slot_free = bar_base + 8u * (1 + 2 * kAttnKS);   // P.V(i) and Q.K^T(i+2) retired       (phase i)
+    const uint32_t s_full = slot_free + 8u;                         // see the MMA issuer                  (phase k)
+    const uint32_t step_end = slot_free + 16u;                      // softmax: prologue (phase 0), step i (phase i+1)
     volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
+    const uint32_t abort_addr = smem_base + L::kAbortOff;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
-    // A launch that follows a failed one on the same status word does nothing.
     __shared__ int prior_failure;
     if (threadIdx.x == 0) prior_failure = p.status != nullptr ? *reinterpret_cast<volatile int*>(p.status) : 0;
     __syncthreads();
-    if (prior_failure != 0) return;                            // uniform across the CTA
+    if (prior_failure != 0) return;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -148,30 +151,25 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int m0 = blockIdx.x * kAttnBM;
     const int b = bh / p.H;
 
-    // key range and block count for this batch entry
-    int valid = p.N;                                           // columns >= valid get -1e6
+    int valid = p.N;
     bool all_masked = false;
     if (p.key_lens != nullptr) {
         valid = p.key_lens[b];
         valid = valid < 0 ? 0 : (valid > p.N ? p.N : valid);
         all_masked = valid == 0;
     }
-    const int k_range = all_masked ? p.N : valid;              // keys that are visited at all
-    const int nblk = (k_range + kAttnBN - 1) / kAttnBN;
+    const int k_range = all_masked ? p.N : valid;
+    const int nblk = (k_range + kAttnBN - 1) / kAttnBN;          // >= 1
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(q_full, 1);
         for (int s = 0; s < kAttnKS; ++s) {
             ptx::mbar_init(k_full(s), 1);
-            ptx::mbar_init(k_empty(s), 1);
             ptx::mbar_init(v_full(s), 1);
-            ptx::mbar_init(v_empty(s), 1);
         }
+        ptx::mbar_init(slot_free, 1);
         ptx::mbar_init(s_full, 1);
-        ptx::mbar_init(s_free, 4);                             // one arrival per softmax warp
-        ptx::mbar_init(p_full(0), 4);
-        ptx::mbar_init(p_full(1), 4);
-        ptx::mbar_init(pv_done, 1);
+        ptx::mbar_init(step_end, 4);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
@@ -188,8 +186,6 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     ptx::tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
-    // Each warpgroup runs in a branch of its own that starts with its register re-budgeting and
-    // ends with the CTA-wide teardown barrier, so no code path mixes two budgets.
     auto teardown_barrier = [&]() {
         ptx::tcgen05_fence_before_sync();
         asm volatile("bar.sync 0, %0;" ::"n"(kAttnThreads) : "memory");
@@ -199,78 +195,71 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (warp == 0) {
             // -------------------------------------------- TMA producer
             if (lane == 0) {
-                bool ok = true;
                 ptx::mbar_arrive_expect_tx(q_full, L::kQBytes);
                 ptx::tma_load_3d(smem_base + L::kQOff, &tmap_q, q_full, 0, m0, bh);
-                int issued = 0;
-                for (int i = 0; ok && i < nblk; ++i) {
-                    const int jb = nblk - 1 - i;
-                    const int s = i % kAttnKS;
-                    const uint32_t ph = (i / kAttnKS) & 1u;
-                    if (!ptx::mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                auto load_kv = [&](int j) {                     // block j (visit order) into slot j % 3
+                    const int jb = nblk - 1 - j;
+                    const int s = j % kAttnKS;
                     ptx::mbar_arrive_expect_tx(k_full(s), L::kKBytes);
                     ptx::tma_load_3d(smem_base + L::kKOff + s * L::kKBytes, &tmap_k, k_full(s), 0, jb * kAttnBN, bh);
-                    if (!ptx::mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(v_full(s), L::kVBytes);
                     ptx::tma_load_3d(smem_base + L::kVOff + s * L::kVBytes, &tmap_v, v_full(s), jb * kAttnBN, 0, bh);
-                    issued = i + 1;
+                };
+                const int first = nblk < kAttnKS ? nblk : kAttnKS;
+                for (int j = 0; j < first; ++j) load_kv(j);
+                for (int i = 0; i + kAttnKS < nblk; ++i) {
+                    // K(i) was consumed before step i, V(i) by P.V(i): both slots i % 3 are free
+                    bounded_wait(slot_free, (uint32_t)i & 1u, abort_addr, 4);
+                    if (*abort_flag != 0) break;                // a wait was abandoned: issue nothing more
+                    load_kv(i + kAttnKS);
                 }
-                if (!ok) {
-                    if (p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (4 << 8));
-                    // bounded grace period for copies still in flight
-                    const int first = issued > kAttnKS ? issued - kAttnKS : 0;
-                    for (int i = first; i < issued; ++i) {
-                        const unsigned long long t0 = ptx::globaltimer_ns();
-                        while (!(ptx::mbar_try_wait(k_full(i % kAttnKS), (i / kAttnKS) & 1u) &&
-                                 ptx::mbar_try_wait(v_full(i % kAttnKS), (i / kAttnKS) & 1u)) &&
-                               ptx::globaltimer_ns() - t0 < 100000000ull) {}
-                    }
+                // (slot_free phases that are never waited on simply complete.)
+                if (*abort_flag != 0) {
+                    // grace period for copies still in flight: they land within microseconds
+                    const unsigned long long t0 = ptx::globaltimer_ns();
+                    while (ptx::globaltimer_ns() - t0 < 50000ull) {}
                 }
             }
         } else if (warp == 1) {
             // -------------------------------------------- MMA issuer
             if (lane == 0) {
-                constexpr uint32_t IDESC = ptx::make_idesc_e4m3(kAttnBM, kAttnBN);   // both GEMMs are M128 N64
+                constexpr uint32_t IDESC = ptx::make_idesc_e4m3(kAttnBM, kAttnBN);
                 const uint64_t q_desc = ptx::make_kmajor_desc(smem_base + L::kQOff, 64);
                 const uint32_t s_tmem = tmem_base;
                 const uint32_t o_tmem = tmem_base + kAttnOCol;
-                bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
-
-                // S = Q . K(i)^T ; S is free once the softmax warps hold block i-1 in registers
-                auto issue_qk = [&](int i) -> bool {
-                    const int s = i % kAttnKS;
-                    if (!ptx::mbar_wait(k_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_flag)) return false;
-                    if (i >= 1 && !ptx::mbar_wait(s_free, (uint32_t)(i - 1) & 1u, abort_flag)) return false;
+                auto issue_qk = [&](int j) {
+                    const int s = j % kAttnKS;
+                    bounded_wait(k_full(s), (uint32_t)(j / kAttnKS) & 1u, abort_addr, 5);
                     ptx::tcgen05_fence_after_sync();
                     const uint64_t k_desc = ptx::make_kmajor_desc(smem_base + L::kKOff + s * L::kKBytes, 64);
 #pragma unroll
                     for (int k = 0; k < kAttnD / 32; ++k)
                         ptx::mma_f8f6f4(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC, k > 0 ? 1u : 0u);
-                    ptx::tcgen05_commit(k_empty(s));
-                    ptx::tcgen05_commit(s_full);
-                    return true;
                 };
-
-                if (ok && nblk > 0) ok = issue_qk(0);
-                for (int i = 0; ok && i < nblk; ++i) {
-                    // scores of the next block first: the softmax warps refill from them mid-step
-                    if (i + 1 < nblk) {
-                        if (!issue_qk(i + 1)) { ok = false; break; }
-                    }
+                // s_full phases: 0 = Q.K^T(0); 1 = Q.K^T(1) (if any); i+2 = P.V(i) and Q.K^T(i+2) (if any).
+                // So phase i+1, which the softmax warps wait for in the middle of step i, says that the
+                // scores of block i+1 are in TMEM AND (i >= 1) that O holds P.V up to block i-1; phase
+                // nblk+1 says that O is complete.
+                bounded_wait(q_full, 0, abort_addr, 5);
+                issue_qk(0);
+                ptx::tcgen05_commit(s_full);
+                bounded_wait(step_end, 0, abort_addr, 5);        // S(0) is in registers
+                if (nblk > 1) issue_qk(1);
+                ptx::tcgen05_commit(s_full);
+                for (int i = 0; i < nblk; ++i) {
                     const int s = i % kAttnKS;
-                    const int pb = i & 1;
-                    if (!ptx::mbar_wait(v_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_flag)) { ok = false; break; }
-                    if (!ptx::mbar_wait(p_full(pb), (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
+                    bounded_wait(step_end, (uint32_t)(i + 1) & 1u, abort_addr, 5);   // P(i) written, O rescaled, S free
+                    bounded_wait(v_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_addr, 5);
                     ptx::tcgen05_fence_after_sync();
-                    const uint64_t p_desc = ptx::make_kmajor_desc(smem_base + L::kPOff + pb * L::kPBytes, 64);
+                    const uint64_t p_desc = ptx::make_kmajor_desc(smem_base + L::kPOff + (i & 1) * L::kPBytes, 64);
                     const uint64_t v_desc = ptx::make_kmajor_desc(smem_base + L::kVOff + s * L::kVBytes, 64);
 #pragma unroll
                     for (int k = 0; k < kAttnBN / 32; ++k)
                         ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
-                    ptx::tcgen05_commit(v_empty(s));
-                    ptx::tcgen05_commit(pv_done);
+                    if (i + 2 < nblk) issue_qk(i + 2);
+                    ptx::tcgen05_commit(s_full);
+                    ptx::tcgen05_commit(slot_free);
                 }
-                if (!ok && p.status != nullptr) atomicExch(p.status, Q8K_STATUS_TIMEOUT | (5 << 8));
             }
         }
         teardown_barrier();
@@ -283,191 +272,139 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         reg_alloc<kAttnRegsSoftmax>();
         // ------------------------------------------------ softmax / O rescale / epilogue
         const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;                      // row of the tile == TMEM lane
+        const int r = quarter * 32 + lane;
         const int row = m0 + r;
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const float c = p.scale_log2;
-        const uint32_t swz = (uint32_t)((r >> 1) & 3);          // 64B swizzle: 16-byte chunk ^= bits [7,9) of the offset
+        const uint32_t swz = (uint32_t)((r >> 1) & 3);
+        // this row's 16-byte chunk ch of P buffer 0 sits at p_a0 ^ (ch << 4) (64B swizzle; the row starts 64-byte aligned)
+        const uint32_t p_a0 = (smem_base + L::kPOff + (uint32_t)r * kAttnBN) | (swz << 4);
 
         float m_run = -INFINITY;
         float l_run = 0.f;
-        bool ok = true;
-        uint32_t cur[2][32];                                    // scores of the block being processed
+        uint32_t cur[2][32];
 
-        if (nblk > 0) {
-            ok = ptx::mbar_wait(s_full, 0, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                ptx::tcgen05_fence_after_sync();
-                ptx::tmem_ld_32x32b_x32(t_lane, cur[0]);
-                ptx::tmem_ld_32x32b_x32(t_lane + 32, cur[1]);
-                ptx::tmem_wait_ld();
-                ptx::tcgen05_fence_before_sync();
-                warp_arrive(s_free, lane);                      // Q.K^T of block 1 may overwrite S
-            }
-        }
+        bounded_wait(s_full, 0, abort_addr, 6);
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_ld_32x32b_x32(t_lane, cur[0]);
+        ptx::tmem_ld_32x32b_x32(t_lane + 32, cur[1]);
+        ptx::tmem_wait_ld();
+        ptx::tcgen05_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(step_end);
 
-#pragma unroll 1
-        for (int i = 0; ok && i < nblk; ++i) {
-            const int jb = nblk - 1 - i;
-            const int col0 = jb * kAttnBN;
-            const int pb = i & 1;
-            const bool need_mask = (col0 + kAttnBN > valid) || (col0 + kAttnBN > p.N);
-            const bool prefetch = i + 1 < nblk;
-            uint8_t* p_row = smem + L::kPOff + pb * L::kPBytes + r * kAttnBN;
-
-            // row max of the (masked) scores; four independent chains of 3-input max
-            float m_blk = -INFINITY;
-            if (need_mask) {
+        // columns >= N get -inf, columns >= key_lens[b] the reference's mask value
+        auto mask_scores = [&](int i) {
+            const int col0 = (nblk - 1 - i) * kAttnBN;
+            if (col0 + kAttnBN > valid || col0 + kAttnBN > p.N) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int col = col0 + h * 32 + j;
-                        float sv = __uint_as_float(cur[h][j]);
-                        sv = col >= p.N ? -INFINITY : (col >= valid ? -1.0e6f : sv);
-                        cur[h][j] = __float_as_uint(sv);
-                        m_blk = fmaxf(m_blk, sv);
+                        const float sv = __uint_as_float(cur[h][j]);
+                        cur[h][j] = __float_as_uint(col >= p.N ? -INFINITY : (col >= valid ? -1.0e6f : sv));
                     }
-            } else {
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            mx[q] = fmax3(mx[q], __uint_as_float(cur[h][j + 2 * q]), __uint_as_float(cur[h][j + 2 * q + 1]));
-                    }
-                m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             }
-            const float m_new = fmaxf(m_run, m_blk);
-            const float m_scaled = m_new == -INFINITY ? 0.f : m_new * c;
-            const float alpha = m_run == -INFINITY ? 0.f : fast_exp2((m_run - m_new) * c);
+        };
 
-            // pv_done is waited on by parity, which only tells phases apart while the waiter is at
-            // most one phase behind.  So every step observes phase i-1 exactly once: here when O
-            // has to be rescaled, otherwise after the exps (where it has long completed).
-            const bool rescale = i > 0 && __any_sync(0xffffffffu, m_new != m_run);
-            if (rescale) {
-                // O is complete once P.V of the previous block has retired
-                ok = ptx::mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                ptx::tcgen05_fence_after_sync();
-#pragma unroll 1
-                for (int h = 0; h < kAttnD / 16; ++h) {
-                    uint32_t orow[16];
-                    __syncwarp();
-                    ptx::tmem_ld_32x32b_x16(t_lane + kAttnOCol + h * 16, orow);
-                    ptx::tmem_wait_ld();
-                    const float2 al2 = make_float2(alpha, alpha);
+        // One step.  UNFUSED: products rounded before the subtraction (batch entries without a
+        // single valid key, where every score is the mask value and 2^0 must come out exactly).
+        auto step = [&](int i, auto unfused_tag, uint32_t pb_off) {
+            constexpr bool UNFUSED = decltype(unfused_tag)::value;
+            if (UNFUSED) mask_scores(i);
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        const float2 m = fmul2(make_float2(__uint_as_float(orow[j]), __uint_as_float(orow[j + 1])), al2);
-                        orow[j] = __float_as_uint(m.x);
-                        orow[j + 1] = __float_as_uint(m.y);
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        mx[q] = fmax3(mx[q], __uint_as_float(cur[h][j + 2 * q]), __uint_as_float(cur[h][j + 2 * q + 1]));
+                }
+            const float m_new = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_run);   // finite: a block has a key < N
+            const float m_scaled = m_new * c;
+            const float alpha = fast_exp2((m_run - m_new) * c);     // first step: 2^-inf = 0
+            const bool rescale = i > 0 && __any_sync(0xffffffffu, m_new != m_run);
+            const float2 c2 = make_float2(c, c);
+            const float2 nm2 = make_float2(-m_scaled, -m_scaled);
+            float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int j = g * 16 + q * 4;
+                        float2 e0, e1;
+                        if (UNFUSED) {
+                            e0 = make_float2(__fsub_rn(__fmul_rn(__uint_as_float(cur[h][j]), c), m_scaled),
+                                             __fsub_rn(__fmul_rn(__uint_as_float(cur[h][j + 1]), c), m_scaled));
+                            e1 = make_float2(__fsub_rn(__fmul_rn(__uint_as_float(cur[h][j + 2]), c), m_scaled),
+                                             __fsub_rn(__fmul_rn(__uint_as_float(cur[h][j + 3]), c), m_scaled));
+                        } else {
+                            e0 = ffma2(make_float2(__uint_as_float(cur[h][j]), __uint_as_float(cur[h][j + 1])), c2, nm2);
+                            e1 = ffma2(make_float2(__uint_as_float(cur[h][j + 2]), __uint_as_float(cur[h][j + 3])), c2, nm2);
+                        }
+                        const float2 p0 = make_float2(fast_exp2(e0.x), fast_exp2(e0.y));
+                        const float2 p1 = make_float2(fast_exp2(e1.x), fast_exp2(e1.y));
+                        sum_a = fadd2(sum_a, p0);
+                        sum_b = fadd2(sum_b, p1);
+                        w[q] = pack4_e4m3(p0.x, p0.y, p1.x, p1.y);
                     }
-                    ptx::tmem_st_32x32b_x16(t_lane + kAttnOCol + h * 16, orow);
+                    st_shared_v4((p_a0 + pb_off) ^ ((uint32_t)(h * 2 + g) << 4), w[0], w[1], w[2], w[3]);
+                }
+                if (h == 0) {
+                    // scores of block i+1 are in TMEM; for i >= 1 also: P.V(i-1) has retired
+                    bounded_wait(s_full, (uint32_t)(i + 1) & 1u, abort_addr, 6);
+                    ptx::tcgen05_fence_after_sync();
+                    if (i + 1 < nblk) ptx::tmem_ld_32x32b_x32(t_lane, cur[0]);
+                }
+            }
+            l_run = l_run * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+            m_run = m_new;
+            if (rescale) {
+                // O *= alpha, two 32-column halves through the registers of the dead second half
+                const float2 al2 = make_float2(alpha, alpha);
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    ptx::tmem_ld_32x32b_x32(t_lane + kAttnOCol + hh * 32, cur[1]);
+                    ptx::tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float2 m = fmul2(make_float2(__uint_as_float(cur[1][j]), __uint_as_float(cur[1][j + 1])), al2);
+                        cur[1][j] = __float_as_uint(m.x);
+                        cur[1][j + 1] = __float_as_uint(m.y);
+                    }
+                    ptx::tmem_st_32x32b_x32(t_lane + kAttnOCol + hh * 32, cur[1]);
                 }
                 ptx::tmem_wait_st();
-                ptx::tcgen05_fence_before_sync();
             }
-            // P[pb] was last read by P.V of block i-2.  That MMA was issued before Q.K^T of block
-            // i, whose completion (s_full, phase i) this warp observed during the previous step,
-            // and MMAs of one thread retire in order -- so the buffer is free without a wait.
+            if (i + 1 < nblk) ptx::tmem_ld_32x32b_x32(t_lane + 32, cur[1]);
+            ptx::fence_proxy_async_smem();                      // P visible to the tensor core's smem reads
+            ptx::tmem_wait_ld();                                // S is free once block i+1 sits in registers
+            ptx::tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(step_end);
+        };
 
-            // half h of `cur` is dead once its exps are done: refill it with block i+1
-            auto refill = [&](int h) -> bool {
-                if (!prefetch) return true;
-                if (h == 0) {
-                    bool got = ptx::mbar_wait(s_full, (uint32_t)(i + 1) & 1u, abort_flag);
-                    if (!__all_sync(0xffffffffu, got)) return false;
-                    ptx::tcgen05_fence_after_sync();
-                }
-                __syncwarp();
-                ptx::tmem_ld_32x32b_x32(t_lane + h * 32, cur[h]);
-                return true;
-            };
-
-            // p = 2^(s*c - m*c), fp32 row sum, e4m3 P into the swizzled smem tile
-            float row_sum = 0.f;
-            if (need_mask) {
-                // Masked scores are -1e6: there the product must be rounded before the subtraction
-                // (as the unfused reference arithmetic does), or the fma's exact product leaves a
-                // residual of up to half an ulp of 1.4e6 in the exponent.
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            float pv[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float sv = __uint_as_float(cur[h][g * 16 + q * 4 + e]);
-                                pv[e] = fast_exp2(__fsub_rn(__fmul_rn(sv, c), m_scaled));
-                                row_sum += pv[e];
-                            }
-                            w[q] = pack4_e4m3(pv[0], pv[1], pv[2], pv[3]);
-                        }
-                        const uint32_t chunk = (uint32_t)(h * 2 + g) ^ swz;
-                        *reinterpret_cast<uint4*>(p_row + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                    if (!refill(h)) { ok = false; break; }
-                }
-            } else {
-                const float2 c2 = make_float2(c, c);
-                const float2 nm2 = make_float2(-m_scaled, -m_scaled);
-                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int j = g * 16 + q * 4;
-                            const float2 e0 = ffma2(make_float2(__uint_as_float(cur[h][j]), __uint_as_float(cur[h][j + 1])), c2, nm2);
-                            const float2 e1 = ffma2(make_float2(__uint_as_float(cur[h][j + 2]), __uint_as_float(cur[h][j + 3])), c2, nm2);
-                            const float2 p0 = make_float2(fast_exp2(e0.x), fast_exp2(e0.y));
-                            const float2 p1 = make_float2(fast_exp2(e1.x), fast_exp2(e1.y));
-                            sum_a = fadd2(sum_a, p0);
-                            sum_b = fadd2(sum_b, p1);
-                            w[q] = pack4_e4m3(p0.x, p0.y, p1.x, p1.y);
-                        }
-                        const uint32_t chunk = (uint32_t)(h * 2 + g) ^ swz;
-                        *reinterpret_cast<uint4*>(p_row + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                    if (!refill(h)) { ok = false; break; }
-                }
-                row_sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        if (!all_masked) {
+            mask_scores(0);                                     // only the block visited first can be partial
+#pragma unroll 1
+            for (int i = 0; i < nblk; i += 2) {
+                step(i, std::false_type{}, 0u);
+                if (i + 1 < nblk) step(i + 1, std::false_type{}, (uint32_t)L::kPBytes);
             }
-            if (!ok) break;
-            if (i > 0 && !rescale) {
-                // keep in step with pv_done (see above); P.V of block i-1 retired during the exps
-                ok = ptx::mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
-            l_run = l_run * alpha + row_sum;
-            m_run = m_new;
-            ptx::fence_proxy_async_smem();                     // P visible to the tensor core's smem reads
-            warp_arrive(p_full(pb), lane);
-            if (prefetch) {
-                ptx::tmem_wait_ld();                           // block i+1 is in registers
-                ptx::tcgen05_fence_before_sync();
-                warp_arrive(s_free, lane);                     // Q.K^T of block i+2 may overwrite S
-            }
+        } else {
+#pragma unroll 1
+            for (int i = 0; i < nblk; ++i) step(i, std::true_type{}, (uint32_t)(i & 1) * L::kPBytes);
         }
 
-        // epilogue: O / l.  The loop has observed pv_done through phase nblk-2, so the parity of
-        // phase nblk-1 is unambiguous here.
-        if (ok && nblk > 0) ok = ptx::mbar_wait(pv_done, (uint32_t)(nblk - 1) & 1u, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            ptx::tcgen05_fence_after_sync();
+        // epilogue: O / l
+        bounded_wait(s_full, (uint32_t)(nblk + 1) & 1u, abort_addr, 7);
+        ptx::tcgen05_fence_after_sync();
+        {
             const float inv = (l_run == 0.f || l_run != l_run) ? 1.f : 1.f / l_run;
             const int64_t out_off = (int64_t)b * p.out_stride_b + (int64_t)(bh - b * p.H) * p.out_stride_h +
                                     (int64_t)row * p.out_stride_s;
@@ -475,16 +412,9 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             for (int h = 0; h < kAttnD / 32; ++h) {
                 uint32_t orow[32];
                 __syncwarp();
-                if (nblk > 0) {
-                    ptx::tmem_ld_32x32b_x32(t_lane + kAttnOCol + h * 32, orow);
-                    ptx::tmem_wait_ld();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) orow[j] = 0u;
-                }
+                ptx::tmem_ld_32x32b_x32(t_lane + kAttnOCol + h * 32, orow);
+                ptx::tmem_wait_ld();
                 if (row < p.M) {
-                  // every destination gets the tile: plain stores, to this GPU's memory or over NVLink to a
-                  // peer's (nothing is read from a peer and nothing here waits on one)
                   for (int dst = 0; dst < p.n_out; ++dst) {
                     if (p.out_e4m3) {
                         uint8_t* o = reinterpret_cast<uint8_t*>(p.outs[dst]) + out_off + h * 32;
@@ -517,16 +447,13 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                   }
                 }
             }
-            // Stores to another GPU are posted: the end of this kernel orders them for work that follows on
-            // THIS GPU, not for a peer that learns of the kernel's end through a collective taking another
-            // route through the switch (an in-switch all-reduce overtook them on 8 GPUs).  A system-scope fence
-            // holds each thread until its stores are visible everywhere, so "kernel finished" implies "landed".
             if (p.n_out > 1) __threadfence_system();
-        } else if (p.status != nullptr && threadIdx.x == 128) {
-            atomicExch(p.status, Q8K_STATUS_TIMEOUT | (6 << 8));
         }
         teardown_barrier();
     }
+    // an abandoned wait anywhere in the CTA is reported through the status word
+    if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr)
+        atomicExch(p.status, Q8K_STATUS_TIMEOUT | (*abort_flag << 8));
 }
 
 // ------------------------------------------------------------------ pre-pass kernels
@@ -702,6 +629,25 @@ attn_prep_v_kernel(const __nv_bfloat16* __restrict__ v, uint8_t* __restrict__ vt
         const uint4 val = *reinterpret_cast<const uint4*>(&tile[d][sc]);
         *reinterpret_cast<uint4*>(vt + ((int64_t)bh * 64 + d) * S_pad + s0 + sc) = val;
     }
+}
+
+// Exercises the bounded wait and the status word without touching any tensor: one warp waits on
+// an mbarrier that nothing ever arrives on, with a limit of `tries` tests.
+__global__ void wait_selftest_kernel(int* status, uint32_t tries) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t abort_word;
+    const uint32_t bar_addr = ptx::smem_u32(&bar);
+    const uint32_t abort_addr = ptx::smem_u32(&abort_word);
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(bar_addr, 1);
+        abort_word = 0;
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    ptx::mbar_wait_bounded(bar_addr, 0, abort_addr, 9, tries);
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_word != 0 && status != nullptr)
+        atomicExch(status, (int)(Q8K_STATUS_TIMEOUT | (abort_word << 8)));
 }
 
 }  // namespace q8k
@@ -883,6 +829,15 @@ extern "C" int q8k_attention_prep_v(const void* v, void* vt8, int B, int H, int 
     dim3 grid((unsigned)((S_kv + 63) / 64), (unsigned)(B * H));
     attn_prep_v_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)v, (uint8_t*)vt8, H, S_kv, s_pad,
                                                               v_stride_b, v_stride_s, v_stride_h);
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_wait_selftest(int* dev_status, unsigned tries, void* stream) {
+    const char* op = "wait_selftest";
+    Q8K_REQUIRE(dev_status != nullptr, Q8K_ERR_INVALID_ARG, "%s: null status word", op);
+    Q8K_REQUIRE(tries >= 1 && tries <= (1u << 16), Q8K_ERR_INVALID_ARG, "%s: tries must be in [1, 65536]", op);
+    wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(dev_status, tries);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }

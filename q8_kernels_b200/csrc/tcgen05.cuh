@@ -96,6 +96,41 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Bounded wait without a result, for kernels whose waits are all on consecutive phases: the first
+// test is inline; the retry loop counts failed tests, looks at the CTA's abort word (a 32-bit word
+// in shared memory, zero while all is well) every 64th of them, so that one abandoned wait ends
+// all the others quickly, and gives up after `limit` tests, storing `site` (non-zero) in the abort
+// word.  Each test may block in hardware for a short, system-defined time.  The caller goes on
+// either way and reports the abort word when the kernel ends.
+constexpr uint32_t kSpinLimit = 1u << 22;
+__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t abort_addr, uint32_t site,
+                                                  uint32_t limit) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 cnt, ab;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
+        "@p bra LAB_DONE;\n\t"
+        "mov.u32 cnt, 0;\n\t"
+        "LAB_WAIT:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
+        "@p bra LAB_DONE;\n\t"
+        "add.u32 cnt, cnt, 1;\n\t"
+        "and.b32 ab, cnt, 63;\n\t"
+        "setp.ne.u32 q, ab, 0;\n\t"
+        "@q bra LAB_WAIT;\n\t"
+        "ld.volatile.shared.u32 ab, [%2];\n\t"
+        "setp.ne.u32 q, ab, 0;\n\t"
+        "@q bra LAB_DONE;\n\t"
+        "setp.lt.u32 q, cnt, %4;\n\t"
+        "@q bra LAB_WAIT;\n\t"
+        "st.volatile.shared.u32 [%2], %3;\n\t"
+        "LAB_DONE:\n\t"
+        "}"
+        ::"r"(bar), "r"(parity), "r"(abort_addr), "r"(site), "r"(limit)
+        : "memory");
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -280,3 +280,28 @@ def test_self_attention_full_shape_sampled(nat, cuda_device):
                             vt[:, heads].contiguous(), ks, None, torch.bfloat16)
     err = Hp.rel_fro(got[:, heads][:, :, rows].float(), ref.float())
     assert err <= TOL, f"rel fro {err:.3e}"
+
+
+def test_abandoned_wait_is_reported_and_the_context_survives(nat, cuda_device):
+    """A wait that nothing satisfies runs into its limit (a warp of a self-test kernel waits on a
+    barrier nobody signals): the kernel returns, the status word carries the timeout code and the
+    site, launches that share the word do nothing until it is cleared, and afterwards the same
+    context computes correct results again."""
+    from q8_kernels_b200 import _lib
+    d = cuda_device
+    q8, k8, vt, ks = _fp8_operands(1, 2, 256, 320, seed=3)
+    q8, k8, vt = q8.to(d), k8.to(d), vt.to(d)
+    want = nat.flash_attention(q8, k8, vt, ks, None, torch.bfloat16)
+    torch.cuda.synchronize()
+    word = _lib.status_word(d)
+    _lib.check(_lib.lib.q8k_wait_selftest(word.data_ptr(), 2000, _lib.stream_ptr(d)), "wait_selftest")
+    torch.cuda.synchronize()
+    assert int(word.item()) == (0x1 | (9 << 8))
+    skipped = nat.flash_attention(q8, k8, vt, ks, None, torch.bfloat16)      # returns at once: status word is set
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.Q8KernelError, match="abandoned a wait"):
+        _lib.check_status(d)                                              # raises and clears the word
+    assert int(word.item()) == 0
+    del skipped
+    again = nat.flash_attention(q8, k8, vt, ks, None, torch.bfloat16)
+    assert torch.equal(again, want)
