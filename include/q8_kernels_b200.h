@@ -254,7 +254,9 @@ Q8K_API int q8k_linear(const void* x, int x_dtype, const void* w, int w_dtype, c
  * cudaMalloc / cudaFree and no allocating library routine.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
  *     with that device current) and caches it; make that first call before any stream capture
- *     is begun on the device.
+ *     is begun on the device.  The cached address belongs to the device's primary context: it does
+ *     not survive a cudaDeviceReset, and `stream` must be a stream of the device that is current
+ *     when the call is made.
  *   - All calls on a device share the one array and it keeps the previous call's contents.  Every
  *     byte a call reads it has written first, so nothing needs clearing, but two calls whose
  *     kernels can overlap on the GPU (different streams without an ordering between them) race

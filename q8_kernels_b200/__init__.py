@@ -8,5 +8,6 @@ or eager fallback.
 """
 from . import _lib, native  # noqa: F401  (loads the native library, fails loudly if absent)
 from . import functional, modules, blocks, utils, graph  # noqa: F401
+from ._lib import Q8KernelError, check_status, read_status  # noqa: F401  (the device status word, see _lib)
 
 __version__ = "0.1.0"

@@ -3,8 +3,9 @@ q8_kernels/blocks/ltx_transformer_block.py:9-58): adaLN-single modulated
 self-attention with RoPE, cross-attention on the text states and a tanh-GELU
 feed-forward, all linears INT8 with Hadamard-rotated per-token activations.
 
-``attn_type`` selects the attention core for both attention layers (the
-reference block never forwards it, so it always runs torch SDPA; default kept).
+``attn_type`` selects the attention core for both attention layers and defaults
+to the FP8 kernel (``"q8_kernels"``); the reference block never forwards it and so
+always runs torch SDPA, which remains available as ``attn_type="torch"``.
 """
 import math
 
@@ -29,7 +30,7 @@ class LTXTransformerBlock(nn.Module):
         self.scale_shift_table = nn.Parameter(torch.randn(6, dim) / dim ** 0.5)
 
     def forward(self, hidden_states, freqs_cis, attention_mask, encoder_hidden_states, encoder_attention_mask,
-                timestep, mm_out_dtype=torch.bfloat16, non_mm_precision=torch.bfloat16, attn_type="torch",
+                timestep, mm_out_dtype=torch.bfloat16, non_mm_precision=torch.bfloat16, attn_type="q8_kernels",
                 head_shard=None, gather_heads=None, fuse=True, peer_buffers=None):
         num_ada_params = self.scale_shift_table.shape[0]
         ada_values = self.scale_shift_table[None, None] + timestep.reshape(

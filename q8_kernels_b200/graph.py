@@ -70,12 +70,16 @@ class _Entry:
 
 class GraphedCallable:
     """See the module docstring.  ``warmup`` eager runs precede each capture; ``pool`` lets several
-    wrappers share one graph memory pool (``torch.cuda.graph_pool_handle()``)."""
+    wrappers share one graph memory pool (``torch.cuda.graph_pool_handle()``).  ``check_status=True``
+    makes every call synchronise and raise if a tensor-core kernel of the replay abandoned a bounded
+    wait (``_lib.check_status``): outputs are undefined in that case.  Off by default, because it
+    costs a device synchronisation per call."""
 
-    def __init__(self, fn: Callable, warmup: int = 1, pool=None):
+    def __init__(self, fn: Callable, warmup: int = 1, pool=None, check_status: bool = False):
         self.fn = fn
         self.warmup = max(1, int(warmup))
         self.pool = pool
+        self.check_status = bool(check_status)
         self._entries: Dict[Tuple, _Entry] = {}
         self._lock = threading.Lock()
         functools.update_wrapper(self, fn.forward if isinstance(fn, torch.nn.Module) else fn)
@@ -117,11 +121,14 @@ class GraphedCallable:
                 if dst.data_ptr() != src.data_ptr():
                     dst.copy_(src)
             e.graph.replay()
+            if self.check_status:
+                from . import _lib
+                _lib.check_status(e.static_inputs[0].device)
             return e.outputs
 
 
-def graphed(fn: Callable, warmup: int = 1, pool=None) -> GraphedCallable:
-    return GraphedCallable(fn, warmup=warmup, pool=pool)
+def graphed(fn: Callable, warmup: int = 1, pool=None, check_status: bool = False) -> GraphedCallable:
+    return GraphedCallable(fn, warmup=warmup, pool=pool, check_status=check_status)
 
 
 def apply_auto_graph(module: torch.nn.Module, filter_func: Callable[[torch.nn.Module], bool] = None,

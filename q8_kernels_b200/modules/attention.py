@@ -5,7 +5,9 @@ change results: ``apply_rope`` runs the RoPE kernel and returns
 ``non_mm_precision`` (the reference's torch fallback returns fp32, which its own
 Hadamard kernel then rejects), and ``head_shard=(rank, world)`` lets a caller
 run the attention core on a slice of the heads (the q/k norm spans all heads, so
-slicing happens after norm and RoPE); the caller gathers the slices.
+slicing happens after norm and RoPE); the caller gathers the slices.  ``attn_type``
+defaults to ``"q8_kernels"`` (the FP8 kernel; the reference's default is ``"torch"``,
+which stays selectable as the eager comparison path).
 """
 import math
 from typing import Optional, Tuple
@@ -78,7 +80,7 @@ class Attention(nn.Module):
         return q, s
 
     def forward(self, hidden_states, freqs_cis=None, encoder_hidden_states=None, attention_mask=None,
-                non_mm_precision=torch.bfloat16, mm_out_dtype=None, apply_qk_hadamard=True, attn_type="torch",
+                non_mm_precision=torch.bfloat16, mm_out_dtype=None, apply_qk_hadamard=True, attn_type="q8_kernels",
                 head_shard: Optional[Tuple[int, int]] = None, gather_heads=None,
                 hidden_states_q=None, out_gate=None, out_residual=None, peer_buffers=None):
         """Reference signature plus: ``head_shard`` / ``gather_heads`` (attention core on a slice of the

@@ -574,11 +574,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, w_scales: torch.Tensor, bias: Optio
     x2 = x.reshape(-1, K).contiguous()
     M, N = x2.shape[0], w.shape[0]
     need = lib.q8k_linear_workspace_bytes(M, K)
-    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < need:
+    if torch.cuda.is_current_stream_capturing():
+        # a buffer allocated during capture belongs to that graph's private pool: never cache it
         ws = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
-        _workspaces[key] = ws
+    else:
+        key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
+            _workspaces[key] = ws
     out_shape = (x.shape[0], x.shape[1], N) if x.dim() == 3 else (1, M, N)
     out = torch.empty(out_shape, dtype=out_type, device=dev)
     with torch.cuda.device(dev):

@@ -95,6 +95,10 @@ class PeerBuffers:
     Nothing here reads from a peer, and no kernel waits on a peer: the only cross-rank wait is the
     NCCL collective, which has the process group's timeout.
 
+    The exported buffer must be a plain ``cudaMalloc`` segment of torch's caching allocator (CUDA IPC
+    cannot export ``expandable_segments`` memory; the export then fails at construction).  ``close()``
+    is collective; the object is a context manager so that it also runs when the body raises.
+
     Checked bit-for-bit against the replicated block on 2 GPUs in stress loops of 120-160 back-to-back
     calls without host synchronisation (ranks in lockstep and deliberately skewed), and on 4 and 8
     GPUs with host-synchronised comparisons.  On 8 GPUs stress loops WITHOUT host synchronisation
@@ -124,6 +128,7 @@ class PeerBuffers:
         self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._turn = 0
         self._opened = []
+        self._closed = False
         handle = (ctypes.c_ubyte * 64)()
         offset = ctypes.c_int64(0)
         with torch.cuda.device(self.device):
@@ -145,8 +150,16 @@ class PeerBuffers:
                 self._base.append(p.value)
         dist.barrier(group=group)                               # every mapping exists before anyone stores
 
+    def __enter__(self) -> "PeerBuffers":
+        return self
+
+    def __exit__(self, exc_type, exc, tb) -> None:
+        self.close()
+
     def next(self, nbytes: int) -> Tuple[torch.Tensor, List[int]]:
         """This call's half: (local uint8 view of ``nbytes`` bytes, its address on every rank, by rank)."""
+        if self._closed:
+            raise RuntimeError("PeerBuffers.next() after close()")
         if nbytes > self.nbytes:
             raise ValueError(f"peer buffers hold {self.nbytes} bytes per call, {nbytes} asked for")
         half = self._turn * self.nbytes
@@ -157,11 +170,19 @@ class PeerBuffers:
         dist.all_reduce(self._flag, group=self.group)
 
     def close(self) -> None:
+        """Collective: every rank calls it.  The local buffer stays alive until every rank has passed
+        the barrier, i.e. until no peer can still store into it; use the object as a context manager so
+        that this also happens on an exception."""
         from ._lib import check, lib
         import ctypes
+        if self._closed:
+            return
+        self._closed = True
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)                          # nobody unmaps while a peer may still store
         with torch.cuda.device(self.device):
             for addr, off in self._opened:
                 check(lib.q8k_ipc_close(ctypes.c_void_p(addr), off), "ipc_close")
         self._opened = []
+        dist.barrier(group=self.group)                          # every mapping of this rank's buffer is gone
+        self._store = None

@@ -11,6 +11,14 @@ Two kinds of file:
   These pin the oracle's RoPE and RoPE-table restatements.  ``ref_convert_state_dict.npz`` is the
   reference's checkpoint converter (q8_kernels/utils/convert_weights.py:23-78) run on a miniature
   diffusers-style state dict with its Hadamard / quantizer calls served by the oracle.
+* ``ref_linear_chain.npz``, ``ref_flash_attn_glue.npz``, ``ref_attention_module.npz``,
+  ``ref_block.npz`` -- the reference's UNMODIFIED Python layer
+  (q8_kernels/functional/{linear,flash_attention}.py, modules/attention.py,
+  blocks/ltx_transformer_block.py and what they import) executed on the CPU over
+  tests/ref_shim.py, i.e. with the fourteen native entry points served by the oracle.
+  They pin everything the glue decides -- which tensor is rotated, quantised, padded,
+  transposed, cast, in what order and with which defaults -- for the oracle's own
+  restatements and for the product's mirrors of those files.
 * ``oracle_*.npz`` -- small seeded cases run through oracle/q8_oracle.py, kept
   so that the GPU kernels are also checked against frozen vectors and a change
   of the oracle shows up as a diff.  The reference has no tests or vectors for
@@ -152,6 +160,117 @@ def reference_convert_fixture() -> None:
     print("reference convert_state_dict:", len(sd), "->", len(out), "tensors")
 
 
+def _save(name: str, **tensors) -> None:
+    """Tensors go in losslessly (see _np) with their torch dtype recorded beside them as ``dtype__<key>``."""
+    arrays = {}
+    for k, v in tensors.items():
+        if isinstance(v, torch.Tensor):
+            arrays[k] = _np(v.detach().contiguous())
+            arrays[f"dtype__{k}"] = np.array(str(v.dtype))
+        else:
+            arrays[k] = np.asarray(v)
+    np.savez_compressed(os.path.join(HERE, name), **arrays)
+
+
+def fill_q8_modules_(module: torch.nn.Module, seed: int) -> None:
+    """Seeded parameters for a reference module tree: Hadamard-rotated INT8 weights of N(0,0.05)
+    matrices, biases N(0,0.05), norm weights ~1, modulation table ~N(0,1/sqrt(dim))."""
+    g = torch.Generator().manual_seed(seed)
+    for mod in module.modules():
+        if type(mod).__name__ == "Q8Linear":
+            w = (torch.randn(mod.out_features, mod.in_features, generator=g) * 0.05).to(torch.bfloat16)
+            wq, ws = O.tokenwise_quant(O.hadamard_transform(w))
+            mod.weight.data = wq
+            mod.scales.data = ws
+            if mod.bias is not None:
+                mod.bias.data = torch.randn(mod.out_features, generator=g) * 0.05
+        elif type(mod).__name__ == "RMSNorm" and mod.weight is not None:
+            mod.weight.data = 1.0 + 0.1 * torch.randn(mod.weight.shape, generator=g)
+        elif hasattr(mod, "scale_shift_table"):
+            t = mod.scale_shift_table
+            mod.scale_shift_table.data = (torch.randn(t.shape, generator=g) / t.shape[1] ** 0.5).to(torch.bfloat16)
+
+
+def reference_glue_fixtures() -> None:
+    """The reference's functional / modules / blocks files, unmodified, over the oracle-backed shim."""
+    import ref_shim
+    ref = ref_shim.load_reference(REF, ref_shim.oracle_backend())
+    RF, RM, RB = ref.functional, ref.modules, ref.blocks
+    E4M3 = torch.float8_e4m3fn
+    bf16 = torch.bfloat16
+
+    # -- functional/linear.py: Q8LinearFunc.forward and FP8LinearFunc.forward
+    a = Hp.activations(40, 256, seed=501).reshape(2, 20, 256)
+    w = Hp.weights(128, 256, seed=502)
+    b = Hp.bias_vec(128, seed=503)
+    wq, sw = O.tokenwise_quant(O.hadamard_transform(w))
+    a8 = O.c10_e4m3(a.float() * 0.5)                                # an e4m3 activation, as attention hands to to_out
+    wf, swf = O.tokenwise_quant(w, E4M3)
+    wfh, swfh = O.tokenwise_quant(O.hadamard_transform(w), E4M3)
+    _save("ref_linear_chain.npz", a=a, w=w, bias=b, a8=a8, wq=wq, sw=sw, wf=wf, swf=swf, wfh=wfh, swfh=swfh,
+          q8_bias_gelu_bf16=RF.linear.q8_linear(a, wq, b, None, sw, True, bf16),
+          q8_plain_default=RF.linear.q8_linear(a, wq, None, None, sw, False, None),
+          q8_from_e4m3_bf16=RF.linear.q8_linear(a8, wq, b, None, sw, False, bf16),
+          q8_16bit_weight_bf16=RF.linear.q8_linear(a, w, b, None, None, False, bf16),
+          fp8_bias_bf16=RF.linear.fp8_linear(a, wf, b, None, swf, False, bf16),
+          fp8_hadamard_bf16=RF.linear.fp8_linear(a, wfh, None, None, swfh, True, bf16),
+          fp8_16bit_weight_bf16=RF.linear.fp8_linear(a, w, b, None, None, False, bf16))
+
+    # -- functional/flash_attention.py: FlashAttnFunc.forward
+    q, k, v = Hp.qkv(2, 2, 77, 64, seed=511)                          # 77 keys: V^T is padded to 80
+    _, kx, vx = Hp.qkv(2, 2, 40, 64, seed=515)
+    mask = torch.tensor([13, 40], dtype=torch.int32)
+    F = RF.flash_attention.flash_attn_func
+    _save("ref_flash_attn_glue.npz", q=q.contiguous(), k=k.contiguous(), v=v.contiguous(), kx=kx.contiguous(),
+          vx=vx.contiguous(), mask=mask,
+          self_hadamard=F(q, k, v, None, None, True),
+          self_plain=F(q, k, v, None, None, False),
+          self_scale=F(q, k, v, 0.2, None, True),
+          cross_masked=F(q, kx, vx, None, mask, True))
+
+    # -- modules/attention.py: Attention.forward
+    dim, heads = 256, 4
+    S, T = 48, 24
+    x = Hp.activations(2 * S, dim, seed=521).reshape(2, S, dim)
+    text = Hp.activations(2 * T, dim, seed=522, outliers=False).reshape(2, T, dim)
+    ang = torch.rand(1, S, dim, generator=Hp.gen(523)) * 6.28
+    cos, sin = ang.cos().expand(2, S, dim).contiguous(), ang.sin().expand(2, S, dim).contiguous()
+    lens = torch.tensor([9, 24], dtype=torch.int32)
+    self_attn = RM.attention.Attention(dim, heads, 64, True, True, qk_rms_norm=True, use_rope=True)
+    cross_attn = RM.attention.Attention(dim, heads, 64, True, True, qk_rms_norm=True, kv_dim=dim, use_rope=False)
+    fill_q8_modules_(self_attn, 524)
+    fill_q8_modules_(cross_attn, 525)
+    with torch.no_grad():
+        out = {
+            # the reference's own default: torch SDPA, rotary embedding on
+            "self_torch": self_attn(x, (cos, sin), None, None, bf16, bf16),
+            # the FP8 kernel path; without the rotary embedding, whose fp32 result the Hadamard entry point rejects
+            "self_q8_norope": self_attn(x, None, text * 0 + x[:, :T], None, bf16, bf16, True, "q8_kernels"),
+            "cross_q8_masked": cross_attn(x, None, text, lens, bf16, bf16, True, "q8_kernels"),
+            "cross_torch_masked": cross_attn(x, None, text, lens, bf16, bf16, True, "torch"),
+        }
+        try:
+            self_attn(x, (cos, sin), None, None, bf16, bf16, True, "q8_kernels")
+            rope_q8 = "ran"
+        except Exception as exc:                                 # noqa: BLE001
+            rope_q8 = f"{type(exc).__name__}: {exc}"
+    _save("ref_attention_module.npz", x=x, text=text, cos=cos, sin=sin, lens=lens,
+          self_rope_q8_outcome=np.array(rope_q8),
+          **{f"self_sd__{k_}": v_ for k_, v_ in self_attn.state_dict().items()},
+          **{f"cross_sd__{k_}": v_ for k_, v_ in cross_attn.state_dict().items()}, **out)
+
+    # -- blocks/ltx_transformer_block.py: LTXTransformerBlock.forward (runs torch SDPA: it never forwards attn_type)
+    blk = RB.ltx_transformer_block.LTXTransformerBlock(dim, heads, 64, dim)
+    fill_q8_modules_(blk, 531)
+    ts = (torch.randn(2, 1, 6 * dim, generator=Hp.gen(532)) * 0.1).to(bf16)
+    with torch.no_grad():
+        y = blk(x, (cos, sin), None, text, lens, ts)
+    _save("ref_block.npz", x=x, text=text, cos=cos, sin=sin, lens=lens, timestep=ts, out=y,
+          **{f"sd__{k_}": v_ for k_, v_ in blk.state_dict().items()})
+    print("reference glue fixtures: linear chain, flash-attention glue, attention module (rope + q8: %s), block"
+          % rope_q8.split(":")[0])
+
+
 def oracle_fixtures() -> None:
     E4M3 = torch.float8_e4m3fn
     # quantizer
@@ -196,6 +315,7 @@ if __name__ == "__main__":
     if REF and os.path.isdir(REF):
         reference_fixtures()
         reference_convert_fixture()
+        reference_glue_fixtures()
     else:
         print("$Q8_REFERENCE does not name a checkout of the reference: reference fixtures left untouched")
     oracle_fixtures()

@@ -22,3 +22,21 @@ def e4m3(a: np.ndarray) -> torch.Tensor:
 
 def t(a: np.ndarray) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def load_typed(name: str):
+    """Fixture written with per-key dtype tags (``dtype__<key>``): key -> torch tensor of that dtype
+    (or the plain numpy value for untagged entries)."""
+    d = load(name)
+    out = {}
+    for k in d.files:
+        if k.startswith("dtype__"):
+            continue
+        tag = f"dtype__{k}"
+        if tag in d.files:
+            dtype = getattr(torch, str(d[tag]).split(".")[-1])
+            x = torch.from_numpy(np.ascontiguousarray(d[k]))
+            out[k] = x.view(dtype) if x.dtype != dtype else x
+        else:
+            out[k] = d[k]
+    return out

@@ -39,7 +39,7 @@ def test_q8_linear_chain(q8, cuda_device, M, K, N, gelu):
 
 
 def test_fp8_linear_config1(q8, cuda_device):
-    """BASELINE config 1: X [1024,2048] ~N(0,1), W [8192,2048] ~N(0,0.02), per-token / per-channel e4m3."""
+    """The CPU-runnable linear case: X [1024,2048] ~N(0,1), W [8192,2048] ~N(0,0.02), per-token / per-channel e4m3."""
     a = Hp.activations(1024, 2048, seed=1, outliers=False)
     w = Hp.weights(8192, 2048, seed=2)
     b = Hp.bias_vec(8192, seed=3)

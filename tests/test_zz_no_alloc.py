@@ -42,22 +42,39 @@ def _call_both(lib, _lib, dev, M, K, N, w_dtype, use_hadamard, gelu, seed):
     rc = lib.q8k_linear_static(*args, out_static.data_ptr(), *tail, status.data_ptr(), stream)
     assert rc == 0, lib.q8k_last_error_detail()
     torch.cuda.synchronize(dev)
-    return out_ws, out_static
+    return out_ws, out_static, (x, wq, ws, bias)
 
 
 def test_linear_static_matches_workspace_variant_twice(cuda_device):
     from q8_kernels_b200 import _lib
     lib = _lib.lib
     # first call: INT8 weights, Hadamard-rotated activations, bias + GELU
-    a, b = _call_both(lib, _lib, cuda_device, 300, 2048, 512, torch.int8, True, True, seed=71)
+    from oracle import q8_oracle as O
+    a, b, (x, wq, ws, bias) = _call_both(lib, _lib, cuda_device, 300, 2048, 512, torch.int8, True, True, seed=71)
     assert not torch.isnan(b.float()).any()
     assert torch.equal(a, b)                                   # same kernels, same inputs: identical bits
     assert Hp.rel_fro(b.float(), a.float()) <= 2e-3
+    # and against the CPU oracle of the same chain (Hadamard, per-token INT8, GEMM, bias, tanh-GELU)
+    want = O.q8_linear(x.cpu(), wq.cpu(), bias.cpu(), None, ws.cpu(), True, torch.bfloat16)[0]
+    assert Hp.rel_fro(b.float(), want.float()) <= 2e-3
     # second call straight after, smaller and of the other kind: it runs over what the first left behind
-    a2, b2 = _call_both(lib, _lib, cuda_device, 96, 256, 128, E4M3, False, False, seed=81)
+    a2, b2, (x2, wq2, ws2, bias2) = _call_both(lib, _lib, cuda_device, 96, 256, 128, E4M3, False, False, seed=81)
     assert not torch.isnan(b2.float()).any()
     assert torch.equal(a2, b2)
     assert Hp.rel_fro(b2.float(), a2.float()) <= 2e-3
+    want2 = O.fp8_linear(x2.cpu(), wq2.cpu(), bias2.cpu(), None, ws2.cpu(), False, torch.bfloat16)[0]
+    assert Hp.rel_fro(b2.float(), want2.float()) <= 2e-3
+    _lib.check_status(cuda_device)
+
+
+@pytest.mark.parametrize("M,K,N", [(8192, 2048, 128), (65536, 64, 128)])
+def test_linear_static_at_the_edge_of_its_capacity(cuda_device, M, K, N):
+    """M*K equal to the scratch size (the quantised rows end exactly where the scale region begins)
+    and M equal to the row limit (the scale region is full): same bits as the workspace variant."""
+    from q8_kernels_b200 import _lib
+    a, b, _ = _call_both(_lib.lib, _lib, cuda_device, M, K, N, torch.int8, True, False, seed=91)
+    assert not torch.isnan(b.float()).any()
+    assert torch.equal(a, b)
     _lib.check_status(cuda_device)
 
 
