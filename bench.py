@@ -382,6 +382,7 @@ def rowwise_cases(q8, dev, rows, dim, g):
     xs = [torch.randn(rows, dim, generator=g, device=dev).to(torch.bfloat16) for _ in range(nset)]
     x8 = [x.to(E4M3) for x in xs[:2]]
     cos = torch.randn(1, rows, dim, generator=g, device=dev)
+    sin = torch.randn(1, rows, dim, generator=g, device=dev)
     mod = [(torch.randn(1, 1, dim, generator=g, device=dev) * 0.1).to(torch.bfloat16) for _ in range(2)]
     state = {"i": 0}
 
@@ -397,8 +398,8 @@ def rowwise_cases(q8, dev, rows, dim, g):
         "norm_modulate_quant_int8": (lambda: nat.norm_modulate_quant(rot().view(1, rows, dim), mod[0], mod[1]),
                                      rows * (3 * dim + 4)),
         "rms_norm": (lambda: nat.rms_norm(rot(), None, None), rows * (4 * dim + 4)),
-        # x in, x out; the [1, rows, dim] fp32 tables are shared by the batch and counted once per call
-        "rope_bf16": (lambda: nat.rope(rot().view(1, rows, dim), cos, cos, torch.bfloat16), rows * (4 + 8) * dim),
+        # x in, x out, and one fp32 cos and one fp32 sin value per element (batch 1: nothing is shared)
+        "rope_bf16": (lambda: nat.rope(rot().view(1, rows, dim), cos, sin, torch.bfloat16), rows * (4 + 8) * dim),
         "fma_e4m3": (lambda: nat.fma_8bit(x8[state["i"] & 1].view(1, rows, dim), mod[0], mod[1], 1.0), rows * 2 * dim),
         "gelu": (lambda: nat.gelu_forward(rot(), None), rows * 4 * dim),
     }

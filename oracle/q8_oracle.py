@@ -207,6 +207,43 @@ def fp8_linear(a, b, bias=None, scale_a=None, scale_b=None, use_hadamard=False, 
     return fp8_mm(a, b, scale_a, scale_b, False, out_dtype, bias=bias)
 
 
+def q8_linear_backward(grad_output, b, scale_b, out_dtype):
+    """Q8LinearFunc.backward (q8_kernels/functional/linear.py:44-53): grad and de-quantised rotated
+    weight re-quantised per row to e4m3, FP8 GEMM, Hadamard back."""
+    g8, gs = tokenwise_quant(grad_output, E4M3)
+    w8, ws = tokenwise_quant((b.to(out_dtype) * scale_b[:, None]).T, E4M3)
+    return hadamard_transform(fp8_mm(g8, w8, gs, ws, False, out_dtype))
+
+
+def fp8_linear_backward(grad_output, b, scale_b, out_dtype, use_hadamard=False):
+    """FP8LinearFunc.backward (q8_kernels/functional/linear.py:161-178)."""
+    g8, gs = tokenwise_quant(grad_output, E4M3)
+    w = (b.to(out_dtype) * scale_b[:, None]).T
+    w8, ws = tokenwise_quant(hadamard_transform(w).T if use_hadamard else w, E4M3)
+    return fp8_mm(g8, w8, gs, ws, False, out_dtype)
+
+
+def q8_linear_lora(a, b, bias, scale_b, lora_a, lora_b, fuse_gelu, out_dtype, grad_output=None):
+    """Q8LinearLora forward and, with ``grad_output``, backward (use_hadamard=True)
+    (q8_kernels/functional/linear.py:56-133).  Returns ``out`` or
+    ``(out, grad_a, grad_lora_a, grad_lora_b)``."""
+    aq, sa = tokenwise_quant(hadamard_transform(a))
+    lora_y = torch.nn.functional.linear(torch.nn.functional.linear(a, lora_a), lora_b)
+    pre = q8_mm(aq, b, sa, scale_b, False, out_dtype, bias=bias) + lora_y
+    out = gelu_forward(pre, out_dtype) if fuse_gelu else pre
+    if grad_output is None:
+        return out
+    g = gelu_backward(pre, grad_output, out_dtype) if fuse_gelu else grad_output
+    g_lb = g @ lora_b
+    w = hadamard_transform((b * scale_b[:, None]).to(out_dtype)).T
+    w8, ws = tokenwise_quant(w, E4M3)
+    g8, gs = tokenwise_quant(g, E4M3)
+    grad_a = fp8_mm(g8, w8, gs, ws, False, out_dtype) + g_lb @ lora_a
+    # per-batch gradients of the factors; autograd sums them down to the parameters' shapes
+    gla, glb = g_lb.transpose(-1, -2) @ a, g.transpose(-1, -2) @ (a @ lora_a.T)
+    return out, grad_a, gla.sum_to_size(lora_a.shape), glb.sum_to_size(lora_b.shape)
+
+
 # --------------------------------------------------------------------------- a8..a11 row-wise ops
 
 def rms_norm(x: torch.Tensor, weights: Optional[torch.Tensor] = None,

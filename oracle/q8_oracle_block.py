@@ -18,9 +18,15 @@ from . import q8_oracle as O
 
 def q8_linear_module(sd: Dict[str, torch.Tensor], prefix: str, x: torch.Tensor, fuse_gelu: bool = False,
                      out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """Q8Linear.forward (q8_kernels/modules/linear.py:31-32)."""
-    return O.q8_linear(x, sd[prefix + "weight"], sd.get(prefix + "bias"), None, sd[prefix + "scales"], fuse_gelu,
-                       out_dtype)
+    """Q8Linear.forward (q8_kernels/modules/linear.py:31-32); with an e4m3 weight the FP8Linear
+    counterpart with Hadamard-rotated per-token e4m3 activations (:129-133 with use_hadamard, plus the
+    GEMM's optional GELU)."""
+    w = sd[prefix + "weight"]
+    if w.dtype == O.E4M3:
+        xq, xs = O.tokenwise_quant(O.hadamard_transform(x), O.E4M3)
+        return O.fp8_mm(xq, w, xs, sd[prefix + "scales"], fuse_gelu, torch.bfloat16 if out_dtype is None else out_dtype,
+                        bias=sd.get(prefix + "bias"))
+    return O.q8_linear(x, w, sd.get(prefix + "bias"), None, sd[prefix + "scales"], fuse_gelu, out_dtype)
 
 
 def attention_module(sd, prefix, hidden_states, freqs_cis=None, encoder_hidden_states=None, attention_mask=None,

@@ -29,6 +29,7 @@ class LTXStackConfig:
     norm_elementwise_affine: bool = False
     positional_embedding_theta: float = 10000.0
     positional_embedding_max_pos: Tuple[int, int, int] = (20, 2048, 2048)
+    linear: str = "int8"                  # "int8": Q8Linear blocks (the reference); "fp8": FP8Linear blocks
 
     @property
     def inner_dim(self) -> int:
@@ -72,7 +73,7 @@ class LTXStack(nn.Module):
         self.caption_projection = nn.Linear(c.caption_channels, c.inner_dim, bias=True)
         self.transformer_blocks = nn.ModuleList([
             LTXTransformerBlock(c.inner_dim, c.num_attention_heads, c.attention_head_dim, c.cross_attention_dim,
-                                c.bias, True, c.norm_elementwise_affine)
+                                c.bias, True, c.norm_elementwise_affine, linear=c.linear)
             for _ in range(c.num_layers)])
 
     def freqs_cis(self, indices_grid: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -95,17 +96,17 @@ class LTXStack(nn.Module):
 
 
 def random_init_(stack: nn.Module, seed: int = 0, device=None) -> nn.Module:
-    """Fill every Q8Linear of a stack (or block) with Hadamard-rotated INT8 weights of
+    """Fill every Q8Linear / FP8Linear of a stack (or block) with Hadamard-rotated 8-bit weights of
     N(0, 0.02) bf16 matrices quantised on the device, biases N(0, 0.02), norm weights ~1."""
-    from ..modules.linear import Q8Linear
+    from ..modules.linear import FP8Linear, Q8Linear
     from .. import native
     g = torch.Generator(device="cpu").manual_seed(seed)
     dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     stack.to(dev)
     for mod in stack.modules():
-        if isinstance(mod, Q8Linear):
+        if isinstance(mod, (Q8Linear, FP8Linear)):
             w = (torch.randn(mod.out_features, mod.in_features, generator=g) * 0.02).to(torch.bfloat16).to(dev)
-            wq, ws = native.hadamard_quant(w, 1 / math.sqrt(mod.in_features), torch.int8)
+            wq, ws = native.hadamard_quant(w, 1 / math.sqrt(mod.in_features), mod.weight.dtype)
             mod.weight.data = wq
             mod.scales.data = ws
             if mod.bias is not None:

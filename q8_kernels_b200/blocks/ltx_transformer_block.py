@@ -20,13 +20,18 @@ from ..modules.rms_norm import RMSNorm
 
 
 class LTXTransformerBlock(nn.Module):
-    def __init__(self, dim, num_heads, head_dim, kv_dim, bias=True, use_rope=True, norm_affine=False):
+    def __init__(self, dim, num_heads, head_dim, kv_dim, bias=True, use_rope=True, norm_affine=False, linear="int8"):
+        """``linear``: ``"int8"`` (the reference's block: Q8Linear everywhere) or ``"fp8"`` (the same block
+        built from FP8Linear with Hadamard-rotated per-token e4m3 activations)."""
         super().__init__()
+        self.linear_kind = linear
         self.norm1 = RMSNorm(dim, norm_affine)
-        self.attn1 = Attention(dim, num_heads, head_dim, bias, bias, qk_rms_norm=True, kv_dim=None, use_rope=use_rope)
-        self.attn2 = Attention(dim, num_heads, head_dim, bias, bias, qk_rms_norm=True, kv_dim=kv_dim, use_rope=False)
+        self.attn1 = Attention(dim, num_heads, head_dim, bias, bias, qk_rms_norm=True, kv_dim=None, use_rope=use_rope,
+                               linear=linear)
+        self.attn2 = Attention(dim, num_heads, head_dim, bias, bias, qk_rms_norm=True, kv_dim=kv_dim, use_rope=False,
+                               linear=linear)
         self.norm2 = RMSNorm(dim, norm_affine)
-        self.ff = FeedForward(dim, bias=bias)
+        self.ff = FeedForward(dim, bias=bias, linear=linear)
         self.scale_shift_table = nn.Parameter(torch.randn(6, dim) / dim ** 0.5)
 
     def forward(self, hidden_states, freqs_cis, attention_mask, encoder_hidden_states, encoder_attention_mask,
@@ -46,7 +51,8 @@ class LTXTransformerBlock(nn.Module):
                  and non_mm_precision == torch.bfloat16 and hidden_states.dim() == 3 and timestep.shape[1] == 1
                  and hidden_states.shape[-1] >= 512)
         if fused and fuse:
-            nq = native.norm_modulate_quant(hidden_states, scale_msa, shift_msa)
+            qt = self.ff.proj_down.weight.dtype                  # int8 or e4m3: the activations follow the weights
+            nq = native.norm_modulate_quant(hidden_states, scale_msa, shift_msa, qt)
             hidden_states = self.attn1(None, freqs_cis, None, attention_mask, non_mm_precision, mm_out_dtype,
                                        attn_type=attn_type, head_shard=head_shard, gather_heads=gather_heads,
                                        hidden_states_q=nq, out_gate=gate_msa, out_residual=hidden_states,
@@ -54,9 +60,9 @@ class LTXTransformerBlock(nn.Module):
             hidden_states = self.attn2(hidden_states, freqs_cis=freqs_cis, encoder_hidden_states=encoder_hidden_states,
                                        attention_mask=encoder_attention_mask, non_mm_precision=non_mm_precision,
                                        mm_out_dtype=mm_out_dtype, attn_type=attn_type, out_residual=hidden_states)
-            fq, fs = native.norm_modulate_quant(hidden_states, scale_mlp, shift_mlp)
+            fq, fs = native.norm_modulate_quant(hidden_states, scale_mlp, shift_mlp, qt)
             act = self.ff.act.proj(fq, fs, fuse_gelu=True, out_dtype=mm_out_dtype)
-            aq, as_ = native.hadamard_quant(act, 1 / math.sqrt(act.shape[-1]), torch.int8)
+            aq, as_ = native.hadamard_quant(act, 1 / math.sqrt(act.shape[-1]), qt)
             down = self.ff.proj_down
             return native.mm_gate_residual(aq, down.weight.data, down.bias.data if down.bias is not None else None,
                                            as_, down.scales, gate_mlp, hidden_states)

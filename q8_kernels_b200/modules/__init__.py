@@ -2,7 +2,7 @@
 from .activations import GELU
 from .attention import Attention
 from .ffn import FeedForward
-from .linear import FP8Linear, Q8Linear
+from .linear import FP8Linear, Q8Linear, Q8LinearLora
 from .rms_norm import RMSNorm
 
-__all__ = ["Attention", "FeedForward", "FP8Linear", "GELU", "Q8Linear", "RMSNorm"]
+__all__ = ["Attention", "FeedForward", "FP8Linear", "GELU", "Q8Linear", "Q8LinearLora", "RMSNorm"]

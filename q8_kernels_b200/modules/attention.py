@@ -17,14 +17,14 @@ import torch.nn as nn
 
 from .. import functional as Q8F
 from .. import native
-from .linear import Q8Linear
+from .linear import make_linear
 from .rms_norm import RMSNorm
 
 
 class Attention(nn.Module):
     def __init__(self, query_dim: int, num_heads: int, head_dim: int, bias: bool = False, out_bias: bool = False,
                  out_dim: Optional[int] = None, qk_rms_norm: bool = False, kv_dim: Optional[int] = None,
-                 use_rope: bool = False):
+                 use_rope: bool = False, linear: str = "int8"):
         super().__init__()
         self.num_heads = num_heads
         self.head_dim = head_dim
@@ -39,10 +39,11 @@ class Attention(nn.Module):
         self.use_rope = use_rope
         kv_dim = query_dim if kv_dim is None else kv_dim
         out_dim = query_dim if out_dim is None else out_dim
-        self.to_q = Q8Linear(query_dim, self.inner_dim, bias=bias)
-        self.to_k = Q8Linear(kv_dim, self.inner_dim, bias=bias)
-        self.to_v = Q8Linear(kv_dim, self.inner_dim, bias=bias)
-        self.to_out = Q8Linear(self.inner_dim, out_dim, out_bias)
+        # the reference builds these from Q8Linear; linear="fp8" selects FP8Linear (Hadamard + per-token e4m3)
+        self.to_q = make_linear(linear, query_dim, self.inner_dim, bias=bias)
+        self.to_k = make_linear(linear, kv_dim, self.inner_dim, bias=bias)
+        self.to_v = make_linear(linear, kv_dim, self.inner_dim, bias=bias)
+        self.to_out = make_linear(linear, self.inner_dim, out_dim, out_bias)
 
     def _stacked(self, key, layers):
         """Weights, biases and scales of projections that share an input, stacked along the output
@@ -64,19 +65,19 @@ class Attention(nn.Module):
 
     @staticmethod
     def _mm(xq, w, b, xs, ws):
+        mm, mmb = (native.q8_mm, native.q8_mm_bias) if w.dtype == torch.int8 else (native.fp8_mm, native.fp8_mm_bias)
         if b is not None:
-            return native.q8_mm_bias(xq, w, b, xs, ws, False, torch.bfloat16)
-        return native.q8_mm(xq, w, xs, ws, False, torch.bfloat16)
+            return mmb(xq, w, b, xs, ws, False, torch.bfloat16)
+        return mm(xq, w, xs, ws, False, torch.bfloat16)
 
-    @staticmethod
-    def _quantize_once(x):
-        """Hadamard (scale 1/sqrt(K)) + per-token INT8 quantizer of an activation, as q8_linear
-        applies to a 16-bit / e4m3 input; already-quantised inputs pass through."""
+    def _quantize_once(self, x):
+        """Hadamard (scale 1/sqrt(K)) + per-token quantizer of an activation to the weights' 8-bit type
+        (INT8 as q8_linear applies to a 16-bit / e4m3 input, or e4m3 for FP8 linears)."""
         if x.dtype == torch.int8:
             raise ValueError("Attention expects un-quantised activations")
         if x.dtype == torch.float16:
             x = x.to(torch.bfloat16)
-        q, s = native.hadamard_quant(x, 1 / math.sqrt(x.shape[-1]), torch.int8)
+        q, s = native.hadamard_quant(x, 1 / math.sqrt(x.shape[-1]), self.to_q.weight.dtype)
         return q, s
 
     def forward(self, hidden_states, freqs_cis=None, encoder_hidden_states=None, attention_mask=None,

@@ -11,7 +11,7 @@ Two kinds of file:
   These pin the oracle's RoPE and RoPE-table restatements.  ``ref_convert_state_dict.npz`` is the
   reference's checkpoint converter (q8_kernels/utils/convert_weights.py:23-78) run on a miniature
   diffusers-style state dict with its Hadamard / quantizer calls served by the oracle.
-* ``ref_linear_chain.npz``, ``ref_flash_attn_glue.npz``, ``ref_attention_module.npz``,
+* ``ref_linear_chain.npz``, ``ref_linear_backward.npz``, ``ref_flash_attn_glue.npz``, ``ref_attention_module.npz``,
   ``ref_block.npz`` -- the reference's UNMODIFIED Python layer
   (q8_kernels/functional/{linear,flash_attention}.py, modules/attention.py,
   blocks/ltx_transformer_block.py and what they import) executed on the CPU over
@@ -215,6 +215,21 @@ def reference_glue_fixtures() -> None:
           fp8_bias_bf16=RF.linear.fp8_linear(a, wf, b, None, swf, False, bf16),
           fp8_hadamard_bf16=RF.linear.fp8_linear(a, wfh, None, None, swfh, True, bf16),
           fp8_16bit_weight_bf16=RF.linear.fp8_linear(a, w, b, None, None, False, bf16))
+
+    # -- functional/linear.py, training side: Q8LinearFunc.backward, FP8LinearFunc.backward, Q8LinearLora
+    g = (torch.randn(2, 20, 128, generator=Hp.gen(504)) * 0.1).to(bf16)
+    a_q8 = a.clone().requires_grad_(True)
+    RF.linear.q8_linear(a_q8, wq, b, None, sw, False, bf16).backward(g)
+    a_f8 = a.clone().requires_grad_(True)
+    RF.linear.fp8_linear(a_f8, wf, b, None, swf, False, bf16).backward(g)
+    la = (torch.randn(8, 256, generator=Hp.gen(505)) / 8).to(bf16).requires_grad_(True)
+    lb = (torch.randn(128, 8, generator=Hp.gen(506)) * 0.1).to(bf16).requires_grad_(True)
+    a_lo = a.clone().requires_grad_(True)
+    y_lo = RF.linear.q8_linear_lora(a_lo, wq, b, None, sw, la, lb, True, True, bf16)
+    y_lo.backward(g)
+    _save("ref_linear_backward.npz", a=a, bias=b, wq=wq, sw=sw, wf=wf, swf=swf, g=g, lora_a=la.detach(),
+          lora_b=lb.detach(), q8_grad_a=a_q8.grad, fp8_grad_a=a_f8.grad, lora_out=y_lo.detach(),
+          lora_grad_a=a_lo.grad, lora_grad_lora_a=la.grad, lora_grad_lora_b=lb.grad)
 
     # -- functional/flash_attention.py: FlashAttnFunc.forward
     q, k, v = Hp.qkv(2, 2, 77, 64, seed=511)                          # 77 keys: V^T is padded to 80

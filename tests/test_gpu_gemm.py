@@ -131,6 +131,24 @@ def test_gemm_full_dit_shapes_properties(nat, cuda_device, kind, K, N):
     assert Hp.rel_fro(col_got, col_ref) < 5e-3                          # bf16 output rounding accumulates over 6144 rows
 
 
+@pytest.mark.parametrize("kind", ["int8", "fp8"])
+@pytest.mark.parametrize("K,N", [(2048, 8192), (8192, 2048)])
+def test_gemm_four_videos_of_tokens_sampled(nat, cuda_device, kind, K, N):
+    """M = 24576 (four videos): sampled rows against the oracle, bias + tanh-GELU, bf16 out; plus exact
+    power-of-two linearity of the whole bias-free output in the row scales."""
+    M = 24576
+    aq, sa, wq, sw, bias = _operands(M, N, K, kind, seed=3 * K + N)
+    dev = cuda_device
+    got = _run(nat, dev, kind, aq, sa, wq, sw, bias, True, torch.bfloat16)
+    rows = torch.cat([torch.randperm(M, generator=Hp.gen(2))[:60], torch.tensor([0, 255, 256, M - 257, M - 1])])
+    ref = _oracle(kind, aq[rows], sa[rows], wq, sw, bias, True, torch.bfloat16)
+    err = Hp.rel_fro(got[0, rows.to(dev)].float(), ref[0].float())
+    assert err <= TOL, f"rel fro {err:.3e}"
+    plain = _run(nat, dev, kind, aq, sa, wq, sw, None, False, torch.bfloat16)
+    halved = _run(nat, dev, kind, aq, sa * 0.5, wq, sw, None, False, torch.bfloat16)
+    assert torch.equal(halved.float() * 2, plain.float())
+
+
 def test_gemm_argument_errors(nat, cuda_device):
     from q8_kernels_b200._lib import Q8KernelError
     d = cuda_device

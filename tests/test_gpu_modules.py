@@ -287,3 +287,81 @@ def test_fp8_linear_from_linear_at_t5_encoder_dims(cuda_device, in_f, out_f, use
     ref = O.fp8_linear(x, wq, None, None, sw, use_hadamard, torch.bfloat16)
     assert y.shape == (1, 48, out_f) and y.dtype == torch.bfloat16
     assert Hp.rel_fro(y.float(), ref.float()) <= TOL
+
+
+def test_fp8_linear_variant_of_the_block(q8, cuda_device):
+    """The same block built from FP8Linear (Hadamard-rotated per-token e4m3 activations, e4m3
+    weights): fused path against the op-by-op path, and both against the oracle block run on the
+    same e4m3 weights."""
+    dim, heads, S, T = 512, 8, 192, 48
+    d = cuda_device
+    cfg = q8.blocks.LTXStackConfig(num_layers=1, num_attention_heads=heads, attention_head_dim=64,
+                                   cross_attention_dim=dim, caption_channels=64, linear="fp8")
+    stack = q8.blocks.random_init_(q8.blocks.LTXStack(cfg), seed=41, device=d)
+    blk = stack.transformer_blocks[0]
+    assert blk.attn1.to_q.weight.dtype == E4M3 and blk.ff.proj_down.weight.dtype == E4M3
+    g = Hp.gen(42)
+    x = torch.randn(2, S, dim, generator=g).to(torch.bfloat16)
+    text = torch.randn(2, T, dim, generator=g).to(torch.bfloat16)
+    ts = (torch.randn(2, 1, 6 * dim, generator=g) * 0.1).to(torch.bfloat16)
+    grid = torch.stack(torch.meshgrid(torch.arange(4), torch.arange(6), torch.arange(8), indexing="ij"), 0)
+    cos, sin = O.precompute_freqs_cis(grid.reshape(1, 3, -1).float(), dim=dim)
+    lens = torch.tensor([17, 48], dtype=torch.int32)
+    args = (x.to(d), (cos.to(d), sin.to(d)), None, text.to(d), lens.to(d), ts.to(d))
+    with torch.no_grad():
+        fused = blk(*args)
+        plain = blk(*args, fuse=False)
+    sd = {k: v.detach().cpu() for k, v in blk.state_dict().items()}
+    ref = OB.ltx_block(sd, x, (cos, sin), None, text, lens, ts, num_heads=heads, head_dim=64)
+    assert Hp.rel_fro(fused.float(), plain.float()) < 5e-3
+    for name, got in (("fused", fused), ("op by op", plain)):
+        err = Hp.rel_fro(got.float(), ref.float())
+        assert err < 2e-2, f"{name}: rel fro {err:.3e}"
+
+
+def test_full_size_block_fused_path_equals_op_by_op_path(q8, cuda_device):
+    """The block at its real size (hidden 2048, 32 x 64 heads, FFN 8192, 6144 tokens, 128 text tokens):
+    the fused path (norm + modulation + Hadamard + quantizer producers, stacked QKV, fused q/k prep,
+    gate/residual epilogues) against the op-by-op path of the reference.  No oracle needed: both run
+    the same arithmetic, only the mean-square summation order of the q/k norm differs."""
+    d = cuda_device
+    cfg = q8.blocks.LTXStackConfig(num_layers=1)
+    stack = q8.blocks.random_init_(q8.blocks.LTXStack(cfg), seed=51, device=d)
+    blk = stack.transformer_blocks[0]
+    g = torch.Generator(device="cpu").manual_seed(52)
+    S, T = 6144, 128
+    x = torch.randn(1, S, cfg.inner_dim, generator=g).to(torch.bfloat16).to(d)
+    text = torch.randn(1, T, cfg.inner_dim, generator=g).to(torch.bfloat16).to(d)
+    ts = (torch.randn(1, 1, 6 * cfg.inner_dim, generator=g) * 0.1).to(torch.bfloat16).to(d)
+    freqs = stack.freqs_cis(q8.blocks.latent_grid(16, 16, 24, device=d))
+    lens = torch.tensor([97], dtype=torch.int32, device=d)
+    with torch.no_grad():
+        fused = blk(x, freqs, None, text, lens, ts)
+        plain = blk(x, freqs, None, text, lens, ts, fuse=False)
+    assert torch.isfinite(fused.float()).all()
+    err = Hp.rel_fro(fused.float(), plain.float())
+    # measured 7.7e-3: a last-bit difference of 1/rms flips a few e4m3 q/k bytes, and over 6144 keys and the
+    # re-quantisation of every later activation that grows to bf16-level noise; the bar of the oracle comparison
+    assert err < 1.5e-2, f"rel fro {err:.3e}"
+
+
+def test_full_stack_eager_equals_graph_replay(q8, cuda_device):
+    """All 28 blocks on one video: finite output, and the CUDA-graph replay reproduces the eager run
+    bit for bit."""
+    d = cuda_device
+    cfg = q8.blocks.LTXStackConfig()
+    stack = q8.blocks.random_init_(q8.blocks.LTXStack(cfg), seed=61, device=d)
+    g = torch.Generator(device="cpu").manual_seed(62)
+    S, T = 6144, 128
+    x = torch.randn(1, S, cfg.inner_dim, generator=g).to(torch.bfloat16).to(d)
+    text = torch.randn(1, T, cfg.caption_channels, generator=g).to(torch.bfloat16).to(d)
+    ts = (torch.randn(1, 1, 6 * cfg.inner_dim, generator=g) * 0.1).to(torch.bfloat16).to(d)
+    grid = q8.blocks.latent_grid(16, 16, 24, device=d)
+    lens = torch.tensor([97], dtype=torch.int32, device=d)
+    with torch.no_grad():
+        eager = stack(x, grid, text, lens, ts).clone()
+        fn = q8.graph.graphed(lambda *a: stack(*a), check_status=True)
+        replay1 = fn(x, grid, text, lens, ts).clone()
+        replay2 = fn(x, grid, text, lens, ts)
+    assert torch.isfinite(eager.float()).all()
+    assert torch.equal(eager, replay1) and torch.equal(eager, replay2)

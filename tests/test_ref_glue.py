@@ -52,6 +52,20 @@ def test_oracle_linear_chains_equal_the_reference_functions():
         Hp.assert_bit_equal(got, d[name], name)
 
 
+def test_oracle_linear_backward_equals_the_reference_autograd():
+    """Q8LinearFunc.backward, FP8LinearFunc.backward and the LoRA linear (forward, activation gradient,
+    gradients of both low-rank factors) of the reference, run through its own autograd."""
+    d = G.load_typed("ref_linear_backward.npz")
+    g = d["g"]
+    Hp.assert_bit_equal(O.q8_linear_backward(g, d["wq"], d["sw"], BF16), d["q8_grad_a"], "q8 grad")
+    Hp.assert_bit_equal(O.fp8_linear_backward(g, d["wf"], d["swf"], BF16), d["fp8_grad_a"], "fp8 grad")
+    out, ga, gla, glb = O.q8_linear_lora(d["a"], d["wq"], d["bias"], d["sw"], d["lora_a"], d["lora_b"], True, BF16, g)
+    Hp.assert_bit_equal(out, d["lora_out"], "lora out")
+    Hp.assert_bit_equal(ga, d["lora_grad_a"], "lora grad a")
+    Hp.assert_bit_equal(gla, d["lora_grad_lora_a"], "lora grad lora_a")
+    Hp.assert_bit_equal(glb, d["lora_grad_lora_b"], "lora grad lora_b")
+
+
 def test_oracle_flash_attn_func_equals_the_reference_function():
     d = G.load_typed("ref_flash_attn_glue.npz")
     q, k, v = d["q"], d["k"], d["v"]
@@ -134,6 +148,35 @@ def test_product_linear_functions_against_the_reference_glue(cuda_device):
 
 
 @pytest.mark.gpu
+def test_product_linear_backward_against_the_reference_autograd(cuda_device):
+    import q8_kernels_b200 as q8
+    L = q8.functional.linear
+    d = {k: (v.to(cuda_device) if isinstance(v, torch.Tensor) else v) for k, v in G.load_typed("ref_linear_backward.npz").items()}
+    g = d["g"]
+    a = d["a"].clone().requires_grad_(True)
+    L.q8_linear(a, d["wq"], d["bias"], None, d["sw"], False, BF16).backward(g)
+    assert Hp.rel_fro(a.grad.float(), d["q8_grad_a"].float()) <= 4e-3
+    a = d["a"].clone().requires_grad_(True)
+    L.fp8_linear(a, d["wf"], d["bias"], None, d["swf"], False, BF16).backward(g)
+    assert Hp.rel_fro(a.grad.float(), d["fp8_grad_a"].float()) <= 4e-3
+    # the LoRA module: frozen INT8 base + trainable low-rank factors
+    lin = q8.modules.Q8LinearLora(256, 128, 8, bias=True, device=cuda_device)
+    lin.weight.data, lin.scales.data, lin.bias.data = d["wq"], d["sw"], d["bias"]
+    lin.lora_a.data, lin.lora_b.data = d["lora_a"].clone(), d["lora_b"].clone()
+    a = d["a"].clone().requires_grad_(True)
+    y = lin(a, fuse_gelu=True, out_dtype=BF16)
+    y.backward(g)
+    assert Hp.rel_fro(y.float(), d["lora_out"].float()) <= 4e-3
+    assert Hp.rel_fro(a.grad.float(), d["lora_grad_a"].float()) <= 6e-3
+    assert Hp.rel_fro(lin.lora_a.grad.float(), d["lora_grad_lora_a"].float()) <= 1e-2
+    assert Hp.rel_fro(lin.lora_b.grad.float(), d["lora_grad_lora_b"].float()) <= 1e-2
+    # without a gradient request the call takes the inference path and gives the same forward values
+    with torch.no_grad():
+        y2 = lin(d["a"], fuse_gelu=True, out_dtype=BF16)
+    assert torch.equal(y2, y.detach())
+
+
+@pytest.mark.gpu
 def test_product_flash_attn_func_against_the_reference_glue(cuda_device):
     import q8_kernels_b200.functional as Q8F
     d = {k: (v.to(cuda_device) if isinstance(v, torch.Tensor) else v) for k, v in G.load_typed("ref_flash_attn_glue.npz").items()}
@@ -191,6 +234,7 @@ def test_product_block_against_the_reference_block(cuda_device):
     sd = {k: v.to(dev) for k, v in _sd(d, "sd__").items()}
     missing, unexpected = blk.load_state_dict(sd, strict=True)
     assert not missing and not unexpected                     # the reference's state dict loads as it is
+    blk.scale_shift_table.data = blk.scale_shift_table.data.to(BF16)   # a freshly built block holds the table in fp32
     args = (d["x"].to(dev), (d["cos"].to(dev), d["sin"].to(dev)), None, d["text"].to(dev), d["lens"].to(dev),
             d["timestep"].to(dev))
     with torch.no_grad():
