@@ -292,10 +292,27 @@ __device__ __forceinline__ uint8_t quantize_fast(float y) {
     else return float_to_e4m3_c10(y);
 }
 
+// Four quantised bytes from four fp32 values, lowest address first.  INT8: round half away from zero
+// (one add + truncation each) and three byte permutes.  E4M3: two packed saturating conversions and
+// one permute; the caller guarantees |y| <= 448 (1 + 2^-23) for finite rows (y = v * (448 / amax) with
+// |v| <= amax), where the saturating cast and the c10 cast (overflow -> NaN beyond 464) agree, and a
+// NaN stays a NaN in both.
+template <typename Tq>
+__device__ __forceinline__ uint32_t quantize_pack4(float y0, float y1, float y2, float y3) {
+    if constexpr (std::is_same_v<Tq, int8_t>) {
+        const uint32_t q0 = (uint32_t)round_half_away_int(y0), q1 = (uint32_t)round_half_away_int(y1);
+        const uint32_t q2 = (uint32_t)round_half_away_int(y2), q3 = (uint32_t)round_half_away_int(y3);
+        return __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+    } else {
+        return (uint32_t)float2_to_e4m3x2_sat(y0, y1) | ((uint32_t)float2_to_e4m3x2_sat(y2, y3) << 16);
+    }
+}
+
 // NORM_MOD adds the block's pre-linear prologue in front of the transform, with the bf16 roundings
 // of the separate ops it replaces: n = bf16(x * rsqrt(mean x^2)); u = bf16(bf16(n * bf16(1 + s)) + h)
 // where s, h are the per-batch modulation rows (bf16 [rows / rows_per_mod, dim]).
-template <typename Tin, typename Tout, int LOG_N, int LOG_V, int ROWS, Epilogue EPI, bool NORM_MOD = false>
+// FULL: dim == 2^LOG_N, so no element of a row needs a bounds test.
+template <typename Tin, typename Tout, int LOG_N, int LOG_V, int ROWS, Epilogue EPI, bool NORM_MOD = false, bool FULL = false>
 __global__ void __launch_bounds__(ROWS << (LOG_N - LOG_V))
 hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __restrict__ scales,
                     int64_t rows, int dim, int64_t x_row_stride, float scale,
@@ -333,7 +350,7 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
         for (int k = 0; k < ITEMS; ++k) {
             const int item = t + k * T;
             Item val;
-            if (row_ok && item * 8 < dim) val = *reinterpret_cast<const Item*>(xr + item * 8);
+            if (row_ok && (FULL || item * 8 < dim)) val = *reinterpret_cast<const Item*>(xr + item * 8);
             else memset(&val, 0, sizeof(val));
             stage[item ^ ((item / ITEMS) & (ITEMS - 1))] = val;   // spread a thread's ITEMS reads over the banks
         }
@@ -373,7 +390,7 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
         const __nv_bfloat16* sh = mod_shift + mrow * dim + t * V;
 #pragma unroll
         for (int k = 0; k < ITEMS; ++k) {
-            if (t * V + k * 8 < dim) {
+            if (FULL || t * V + k * 8 < dim) {
                 float s8[8], h8[8];
                 load_vec<__nv_bfloat16, 8>(sc + k * 8, s8);
                 load_vec<__nv_bfloat16, 8>(sh + k * 8, h8);
@@ -428,7 +445,7 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
             const int e = LF::elem(t, j);
 #pragma unroll
             for (int pc = 0; pc < C / PIECE; ++pc) {
-                if (row_ok && e + pc * PIECE < dim) {
+                if (row_ok && (FULL || e + pc * PIECE < dim)) {
                     float o[PIECE];
 #pragma unroll
                     for (int i = 0; i < PIECE; ++i) o[i] = v[j * C + pc * PIECE + i];
@@ -441,14 +458,14 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
         float amax = 0.f;
 #pragma unroll
         for (int j = 0; j < LF::G; ++j) {
-            const bool in = LF::elem(t, j) < dim;              // dim % 8 == 0: a run of <= 8 is all in or all out
+            const bool in = FULL || LF::elem(t, j) < dim;      // dim % 8 == 0: a run of <= 8 is all in or all out
             float m = 0.f;
 #pragma unroll
             for (int i = 0; i < C; i += 2) {
                 const float2 rt = round_through2<Tin>(v[j * C + i], v[j * C + i + 1]);
                 v[j * C + i] = rt.x;
                 v[j * C + i + 1] = rt.y;
-                if (C <= 8 || LF::elem(t, j) + (i & ~7) < dim) m = fmaxf(m, fmaxf(fabsf(rt.x), fabsf(rt.y)));
+                if (FULL || C <= 8 || LF::elem(t, j) + (i & ~7) < dim) m = fmaxf(m, fmaxf(fabsf(rt.x), fabsf(rt.y)));
             }
             if (C > 8 || in) amax = fmaxf(amax, m);
         }
@@ -472,15 +489,24 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
             const int e = LF::elem(t, j);
 #pragma unroll
             for (int pc = 0; pc < C / PIECE; ++pc) {
-                if (row_ok && e + pc * PIECE < dim) {
+                if (row_ok && (FULL || e + pc * PIECE < dim)) {
                     using BV = typename ByteVec<PIECE>::type;
-                    union { BV vec; uint8_t b[PIECE]; } u;
+                    union { BV vec; uint8_t b[PIECE]; uint32_t w[PIECE >= 4 ? PIECE / 4 : 1]; } u;
+                    const float2 q2 = make_float2(qmul, qmul);
+                    if constexpr (PIECE >= 4) {
 #pragma unroll
-                    for (int i = 0; i < PIECE; i += 2) {
-                        const float2 y = fmul2(make_float2(v[j * C + pc * PIECE + i], v[j * C + pc * PIECE + i + 1]),
-                                               make_float2(qmul, qmul));
-                        u.b[i] = quantize_fast<Tout>(y.x);
-                        u.b[i + 1] = quantize_fast<Tout>(y.y);
+                        for (int i = 0; i < PIECE; i += 4) {
+                            const float2 y0 = fmul2(make_float2(v[j * C + pc * PIECE + i], v[j * C + pc * PIECE + i + 1]), q2);
+                            const float2 y1 = fmul2(make_float2(v[j * C + pc * PIECE + i + 2], v[j * C + pc * PIECE + i + 3]), q2);
+                            u.w[i / 4] = quantize_pack4<Tout>(y0.x, y0.y, y1.x, y1.y);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < PIECE; i += 2) {
+                            const float2 y = fmul2(make_float2(v[j * C + pc * PIECE + i], v[j * C + pc * PIECE + i + 1]), q2);
+                            u.b[i] = quantize_fast<Tout>(y.x);
+                            u.b[i + 1] = quantize_fast<Tout>(y.y);
+                        }
                     }
                     *reinterpret_cast<BV*>(reinterpret_cast<uint8_t*>(outr) + e + pc * PIECE) = u.vec;
                 }
@@ -508,7 +534,8 @@ static int launch_hadamard(const void* x, void* out, float* scales, int64_t rows
         if (log_n > 14) { set_error_detail("%s: dim %d exceeds 16384", op, dim); return Q8K_ERR_UNSUPPORTED; }
 #define Q8K_HR(LN, LV, NR)                                                                                \
     case LN: {                                                                                            \
-        auto kern = hadamard_row_kernel<Tin, Tout, LN, LV, NR, EPI>;                                      \
+        auto kern = dim == (1 << LN) ? hadamard_row_kernel<Tin, Tout, LN, LV, NR, EPI, false, true>       \
+                                     : hadamard_row_kernel<Tin, Tout, LN, LV, NR, EPI, false, false>;     \
         constexpr int smem = NR * (1 << LN) * (int)sizeof(float);                                         \
         if (smem > 48 * 1024)                                                                             \
             Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));   \
@@ -543,7 +570,8 @@ static int launch_norm_mod_quant(const void* x, const void* mod_scale, const voi
     Tout* o = (Tout*)q;
 #define Q8K_NM(LN, LV, NR)                                                                                \
     case LN: {                                                                                            \
-        auto kern = hadamard_row_kernel<__nv_bfloat16, Tout, LN, LV, NR, Epilogue::Quant, true>;          \
+        auto kern = dim == (1 << LN) ? hadamard_row_kernel<__nv_bfloat16, Tout, LN, LV, NR, Epilogue::Quant, true, true>  \
+                                     : hadamard_row_kernel<__nv_bfloat16, Tout, LN, LV, NR, Epilogue::Quant, true, false>; \
         constexpr int smem = NR * (1 << LN) * (int)sizeof(float);                                         \
         if (smem > 48 * 1024)                                                                             \
             Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));   \
