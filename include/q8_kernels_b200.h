@@ -190,6 +190,20 @@ Q8K_API int q8k_flash_attention_multi_out(const void* q, const void* k, const vo
                                   int64_t out_stride_h, int64_t out_stride_s, float softmax_scale,
                                   const int* key_lens, int* dev_status, void* stream);
 
+/* q8k_flash_attention_multi_out with V given as ROWS, v [B,H,N,64] e4m3 (the layout of k; no transpose, no
+ * padding of the key dim): the tensor core reads the V tile as an MN-major operand.  Same arithmetic, same
+ * bits as the transposed form.  This is what the attention module calls; the transposed entry points above
+ * keep the reference's layout (q8_kernels/functional/flash_attention.py:40-48 builds it).                 */
+Q8K_API int q8k_flash_attention_v_rows(const void* q, const void* k, const void* v, void* const* outs, int n_out,
+                               int out_dtype, int B, int H, int M, int N, int64_t out_stride_b,
+                               int64_t out_stride_h, int64_t out_stride_s, float softmax_scale,
+                               const int* key_lens, int* dev_status, void* stream);
+
+/* bf16 [B,H,S,64] view (element strides, last dim contiguous) -> e4m3 [B,H,S,64] contiguous, c10-style cast
+ * (the `.to(float8_e4m3fn)` of q8_kernels/functional/flash_attention.py:47-48 without the transpose).     */
+Q8K_API int q8k_attention_cast_rows(const void* x, void* out8, int B, int H, int S, int64_t stride_b, int64_t stride_s,
+                            int64_t stride_h, void* stream);
+
 /* Set-up helpers for peer destinations (host side, no kernel): export the CUDA IPC handle of the device
  * allocation that contains ptr plus ptr's offset in it; map such an allocation of another process into this
  * one with the calling thread's current device (peer access is enabled by the mapping) and return the

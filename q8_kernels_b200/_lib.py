@@ -56,6 +56,9 @@ SIGNATURES = {
     "q8k_attention_prep": (_c_int, [_c_ptr] * 6 + [_c_int] * 4 + [_c_i64] * 9 + [_c_int, _c_f32, _c_ptr]),
     "q8k_flash_attention_multi_out": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                _c_int, _c_i64, _c_i64, _c_i64, _c_f32, _c_ptr, _c_ptr, _c_ptr]),
+    "q8k_flash_attention_v_rows": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_int, _c_i64, _c_i64, _c_i64, _c_f32, _c_ptr, _c_ptr, _c_ptr]),
+    "q8k_attention_cast_rows": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_ptr]),
     "q8k_ipc_export": (_c_int, [_c_ptr, _c_ptr, _c_ptr]),
     "q8k_ipc_open": (_c_int, [_c_ptr, _c_i64, _c_ptr]),
     "q8k_ipc_close": (_c_int, [_c_ptr, _c_i64]),

@@ -122,6 +122,10 @@ __device__ __forceinline__ void bounded_wait(uint32_t bar, uint32_t parity, uint
     ptx::mbar_wait_bounded(bar, parity, abort_addr, site, ptx::kSpinLimit);
 }
 
+// V_ROWS = false: V arrives transposed, [B,H,64,ceil16(N)] (the reference's layout), and is the K-major B
+// operand of P.V.  V_ROWS = true: V arrives as rows, [B,H,N,64] like K, is loaded by the same kind of TMA
+// box and read by the tensor core as an MN-major B operand, so no transpose pass is needed.
+template <bool V_ROWS>
 __global__ void __maxnreg__(kAttnRegsLaunch)
 flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -203,7 +207,8 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     ptx::mbar_arrive_expect_tx(k_full(s), L::kKBytes);
                     ptx::tma_load_3d(smem_base + L::kKOff + s * L::kKBytes, &tmap_k, k_full(s), 0, jb * kAttnBN, bh);
                     ptx::mbar_arrive_expect_tx(v_full(s), L::kVBytes);
-                    ptx::tma_load_3d(smem_base + L::kVOff + s * L::kVBytes, &tmap_v, v_full(s), jb * kAttnBN, 0, bh);
+                    if (V_ROWS) ptx::tma_load_3d(smem_base + L::kVOff + s * L::kVBytes, &tmap_v, v_full(s), 0, jb * kAttnBN, bh);
+                    else ptx::tma_load_3d(smem_base + L::kVOff + s * L::kVBytes, &tmap_v, v_full(s), jb * kAttnBN, 0, bh);
                 };
                 const int first = nblk < kAttnKS ? nblk : kAttnKS;
                 for (int j = 0; j < first; ++j) load_kv(j);
@@ -224,6 +229,9 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             // -------------------------------------------- MMA issuer
             if (lane == 0) {
                 constexpr uint32_t IDESC = ptx::make_idesc_e4m3(kAttnBM, kAttnBN);
+                // P.V with V as rows: B operand MN-major (bit 16); its 32-key K slices are 32 rows of 64 bytes apart
+                constexpr uint32_t IDESC_PV = V_ROWS ? (IDESC | (1u << 16)) : IDESC;
+                constexpr uint32_t V_KSTEP = V_ROWS ? (32 * 64) >> 4 : 2;
                 const uint64_t q_desc = ptx::make_kmajor_desc(smem_base + L::kQOff, 64);
                 const uint32_t s_tmem = tmem_base;
                 const uint32_t o_tmem = tmem_base + kAttnOCol;
@@ -255,7 +263,7 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     const uint64_t v_desc = ptx::make_kmajor_desc(smem_base + L::kVOff + s * L::kVBytes, 64);
 #pragma unroll
                     for (int k = 0; k < kAttnBN / 32; ++k)
-                        ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+                        ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + V_KSTEP * k, IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
                     if (i + 2 < nblk) issue_qk(i + 2);
                     ptx::tcgen05_commit(s_full);
                     ptx::tcgen05_commit(slot_free);
@@ -670,10 +678,31 @@ extern "C" int q8k_flash_attention_strided(const void* q, const void* k, const v
                                          out_stride_s, softmax_scale, key_lens, dev_status, stream);
 }
 
+static int launch_flash_attention(bool v_rows, const void* q, const void* k, const void* vt, void* const* outs, int n_out,
+                                  int out_dtype, int B, int H, int M, int N, int64_t out_stride_b,
+                                  int64_t out_stride_h, int64_t out_stride_s, float softmax_scale,
+                                  const int* key_lens, int* dev_status, void* stream);
+
 extern "C" int q8k_flash_attention_multi_out(const void* q, const void* k, const void* vt, void* const* outs, int n_out,
                                              int out_dtype, int B, int H, int M, int N, int64_t out_stride_b,
                                              int64_t out_stride_h, int64_t out_stride_s, float softmax_scale,
                                              const int* key_lens, int* dev_status, void* stream) {
+    return launch_flash_attention(false, q, k, vt, outs, n_out, out_dtype, B, H, M, N, out_stride_b, out_stride_h,
+                                  out_stride_s, softmax_scale, key_lens, dev_status, stream);
+}
+
+extern "C" int q8k_flash_attention_v_rows(const void* q, const void* k, const void* v, void* const* outs, int n_out,
+                                          int out_dtype, int B, int H, int M, int N, int64_t out_stride_b,
+                                          int64_t out_stride_h, int64_t out_stride_s, float softmax_scale,
+                                          const int* key_lens, int* dev_status, void* stream) {
+    return launch_flash_attention(true, q, k, v, outs, n_out, out_dtype, B, H, M, N, out_stride_b, out_stride_h,
+                                  out_stride_s, softmax_scale, key_lens, dev_status, stream);
+}
+
+static int launch_flash_attention(bool v_rows, const void* q, const void* k, const void* vt, void* const* outs, int n_out,
+                                  int out_dtype, int B, int H, int M, int N, int64_t out_stride_b,
+                                  int64_t out_stride_h, int64_t out_stride_s, float softmax_scale,
+                                  const int* key_lens, int* dev_status, void* stream) {
     const char* op = "flash_attention";
     Q8K_REQUIRE(outs != nullptr && n_out >= 1 && n_out <= kAttnMaxOut, Q8K_ERR_INVALID_ARG,
                 "%s: between 1 and %d output destinations", op, kAttnMaxOut);
@@ -707,7 +736,12 @@ extern "C" int q8k_flash_attention_multi_out(const void* q, const void* k, const
         const uint32_t box[3] = {64, (uint32_t)kAttnBN, 1};
         if (int rc = make_byte_tensor_map(&tk, k, 3, dims, strides, box, 64, op)) return rc;
     }
-    {
+    if (v_rows) {                                              // V [B,H,N,64]: the same boxes as K
+        const uint64_t dims[3] = {64, (uint64_t)N, BH};
+        const uint64_t strides[2] = {64, (uint64_t)N * 64};
+        const uint32_t box[3] = {64, (uint32_t)kAttnBN, 1};
+        if (int rc = make_byte_tensor_map(&tv, vt, 3, dims, strides, box, 64, op)) return rc;
+    } else {                                                   // V^T [B,H,64,ceil16(N)]
         const uint64_t dims[3] = {(uint64_t)n_pad, 64, BH};
         const uint64_t strides[2] = {(uint64_t)n_pad, (uint64_t)n_pad * 64};
         const uint32_t box[3] = {(uint32_t)kAttnBN, 64, 1};
@@ -727,14 +761,30 @@ extern "C" int q8k_flash_attention_multi_out(const void* q, const void* k, const
     // The warpgroups re-budget registers with setmaxnreg; an increase blocks until the CTA's pool
     // has room, so the pool the kernel was compiled for must cover the three budgets.
     static_assert(2 * kAttnRegsLaunch == kAttnRegsIo + kAttnRegsSoftmax, "register budgets");
+    auto kern = v_rows ? flash_attn_fp8_kernel<true> : flash_attn_fp8_kernel<false>;
     cudaFuncAttributes fattr;
-    Q8K_CUDA_OK(cudaFuncGetAttributes(&fattr, flash_attn_fp8_kernel));
+    Q8K_CUDA_OK(cudaFuncGetAttributes(&fattr, kern));
     Q8K_REQUIRE(fattr.numRegs >= kAttnRegsLaunch, Q8K_ERR_CUDA,
                 "%s: kernel was built with %d registers per thread, %d needed for the warpgroup budgets", op,
                 fattr.numRegs, kAttnRegsLaunch);
-    Q8K_CUDA_OK(cudaFuncSetAttribute(flash_attn_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::kDynamic));
+    Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::kDynamic));
     dim3 grid((unsigned)((M + kAttnBM - 1) / kAttnBM), (unsigned)BH);
-    flash_attn_fp8_kernel<<<grid, kAttnThreads, AttnSmem::kDynamic, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    kern<<<grid, kAttnThreads, AttnSmem::kDynamic, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+extern "C" int q8k_attention_cast_rows(const void* x, void* out8, int B, int H, int S, int64_t stride_b, int64_t stride_s,
+                                       int64_t stride_h, void* stream) {
+    const char* op = "attention_cast_rows";
+    Q8K_REQUIRE(x && out8, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE(B > 0 && H > 0 && S > 0, Q8K_ERR_INVALID_ARG, "%s: bad shape", op);
+    Q8K_REQUIRE(stride_b % 8 == 0 && stride_s % 8 == 0 && stride_h % 8 == 0 && aligned16(x) && aligned16(out8),
+                Q8K_ERR_INVALID_ARG, "%s: strides must be multiples of 8 elements and pointers 16-byte aligned", op);
+    const int64_t rows = (int64_t)B * S * H;
+    Q8K_REQUIRE((rows + 15) / 16 <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
+    attn_prep_qk_kernel<<<(unsigned)((rows + 15) / 16), 128, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (uint8_t*)out8, B, H, S, stride_b, stride_s, stride_h, 0, 1.0f);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }

@@ -131,7 +131,8 @@ class Attention(nn.Module):
                 q8_ = native.qk_norm_rope_prep(query, self.q_norm.weight, None, heads, True, scale)
                 k8_ = native.qk_norm_rope_prep(kv[..., :C], self.k_norm.weight, None, heads, True, scale)
                 value = kv[..., C:]
-            vt8 = native.attention_prep_v(value.unflatten(-1, (heads, self.head_dim)).transpose(1, 2))
+            # V as rows [B,H,S,64]: the tensor core reads it MN-major, so the reference's transpose is never made
+            vt8 = native.attention_cast_rows(value.unflatten(-1, (heads, self.head_dim)).transpose(1, 2))
             if head_shard is not None:
                 # projections, q/k norm (it spans all heads) and RoPE ran replicated; the attention core
                 # takes this rank's heads and the channel slices are gathered before the output projection
@@ -145,11 +146,12 @@ class Attention(nn.Module):
                     seq = q8_.shape[2]
                     local, addrs = peer_buffers.next(batch_size * seq * self.inner_dim)
                     native.flash_attention_into(q8_, k8_, vt8, 1.0, attention_mask, torch.float8_e4m3fn, addrs,
-                                                self.num_heads, rank * heads)
+                                                self.num_heads, rank * heads, v_rows=True)
                     peer_buffers.barrier()
                     hidden_states = local.view(torch.float8_e4m3fn).view(batch_size, seq, self.inner_dim)
                     return self._project_out(hidden_states, non_mm_precision, mm_out_dtype, out_gate, out_residual)
-            hidden_states = native.flash_attention(q8_, k8_, vt8, 1.0, attention_mask, None, token_major_out=True)
+            hidden_states = native.flash_attention(q8_, k8_, vt8, 1.0, attention_mask, None, token_major_out=True,
+                                                   v_rows=True)
             hidden_states = hidden_states.transpose(1, 2).reshape(batch_size, -1, heads * self.head_dim)
             if head_shard is not None:
                 if gather_heads is None:

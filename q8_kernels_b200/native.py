@@ -372,12 +372,14 @@ def mm_gate_residual(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tens
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,
                     batch_mask: Optional[torch.Tensor] = None,
-                    out_type: Optional[torch.dtype] = None, token_major_out: bool = False) -> torch.Tensor:
+                    out_type: Optional[torch.dtype] = None, token_major_out: bool = False,
+                    v_rows: bool = False) -> torch.Tensor:
     """csrc/flash_attention/flash_attention.cpp:18-48: q [B,H,M,64], k [B,H,N,64],
     v [B,H,64,ceil16(N)] e4m3, optional int32 [B] valid-key counts; the output is
     e4m3 [B,H,M,64] like the reference unless ``out_type`` asks for bfloat16.
     ``token_major_out`` stores the result as [B,M,H,64] and returns its [B,H,M,64] view, so the
-    caller's ``transpose(1,2).reshape(B,M,H*64)`` is free."""
+    caller's ``transpose(1,2).reshape(B,M,H*64)`` is free.  ``v_rows``: v is [B,H,N,64] (rows, like k)
+    instead of the reference's transposed layout; same result, no transpose pass needed."""
     dev = require_cuda(q, k, v, batch_mask)
     if q.dtype != E4M3 or k.dtype != E4M3 or v.dtype != E4M3:
         raise Q8KernelError("flash_attention: q, k, v must be float8_e4m3fn")
@@ -388,7 +390,10 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_s
     if D != 64 or k.shape[3] != 64:
         raise Q8KernelError("flash_attention: head dim must be 64")
     n_pad = (N + 15) // 16 * 16
-    if tuple(v.shape) != (B, H, 64, n_pad) or tuple(k.shape[:2]) != (B, H):
+    if v_rows:
+        if tuple(v.shape) != (B, H, N, 64) or tuple(k.shape[:2]) != (B, H):
+            raise Q8KernelError("flash_attention: with v_rows, v must be [B,H,N,64] like k")
+    elif tuple(v.shape) != (B, H, 64, n_pad) or tuple(k.shape[:2]) != (B, H):
         raise Q8KernelError(f"flash_attention: v must be [B,H,64,{n_pad}] (transposed, keys padded to 16)")
     if batch_mask is not None:
         if batch_mask.dtype != torch.int32:
@@ -405,15 +410,22 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_s
         buf = torch.empty((B, H, M, 64), dtype=out_type, device=dev)
         strides = (H * M * 64, M * 64, 64)
     with torch.cuda.device(dev):
-        check(lib.q8k_flash_attention_strided(ptr(q), ptr(k), ptr(v), ptr(buf), dt(out_type), B, H, M, N, *strides,
-                                              float(softmax_scale), ptr(batch_mask), ptr(_lib.status_word(dev)),
-                                              stream_ptr(dev)), "flash_attention")
+        if v_rows:
+            outs = (ctypes.c_void_p * 1)(buf.data_ptr())
+            check(lib.q8k_flash_attention_v_rows(ptr(q), ptr(k), ptr(v), ctypes.cast(outs, ctypes.c_void_p), 1,
+                                                 dt(out_type), B, H, M, N, *strides, float(softmax_scale),
+                                                 ptr(batch_mask), ptr(_lib.status_word(dev)), stream_ptr(dev)),
+                  "flash_attention")
+        else:
+            check(lib.q8k_flash_attention_strided(ptr(q), ptr(k), ptr(v), ptr(buf), dt(out_type), B, H, M, N, *strides,
+                                                  float(softmax_scale), ptr(batch_mask), ptr(_lib.status_word(dev)),
+                                                  stream_ptr(dev)), "flash_attention")
     return buf.transpose(1, 2) if token_major_out else buf
 
 
 def flash_attention_into(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,
                          batch_mask: Optional[torch.Tensor], out_type: torch.dtype, dest_ptrs: Sequence[int],
-                         total_heads: int, first_head: int) -> None:
+                         total_heads: int, first_head: int, v_rows: bool = False) -> None:
     """Head-sharded attention writing straight into full token-major buffers: q, k, v hold this rank's
     heads ([B,h,M,64] etc.); every address in ``dest_ptrs`` is the start of a [B,M,total_heads,64] buffer
     of ``out_type`` (this GPU's, or a peer's mapped with ``q8k_ipc_open``) and receives heads
@@ -424,8 +436,8 @@ def flash_attention_into(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, soft
     B, h, M, D = q.shape
     N = k.shape[2]
     n_pad = (N + 15) // 16 * 16
-    if D != 64 or tuple(k.shape) != (B, h, N, 64) or tuple(v.shape) != (B, h, 64, n_pad):
-        raise Q8KernelError("flash_attention: q [B,h,M,64], k [B,h,N,64], v [B,h,64,ceil16(N)] expected")
+    if D != 64 or tuple(k.shape) != (B, h, N, 64) or tuple(v.shape) != ((B, h, N, 64) if v_rows else (B, h, 64, n_pad)):
+        raise Q8KernelError("flash_attention: q [B,h,M,64], k [B,h,N,64], v [B,h,64,ceil16(N)] (or [B,h,N,64] with v_rows) expected")
     if not (0 <= first_head and first_head + h <= total_heads):
         raise Q8KernelError("flash_attention: head range outside the destination buffers")
     if not 1 <= len(dest_ptrs) <= 8:
@@ -440,9 +452,9 @@ def flash_attention_into(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, soft
     outs = (ctypes.c_void_p * len(dest_ptrs))(*[int(a) + head_off for a in dest_ptrs])
     strides = (M * total_heads * 64, 64, total_heads * 64)
     with torch.cuda.device(dev):
-        check(lib.q8k_flash_attention_multi_out(ptr(q), ptr(k), ptr(v), ctypes.cast(outs, ctypes.c_void_p), len(dest_ptrs),
-                                                dt(out_type), B, h, M, N, *strides, float(softmax_scale),
-                                                ptr(batch_mask), ptr(_lib.status_word(dev)), stream_ptr(dev)),
+        fn = lib.q8k_flash_attention_v_rows if v_rows else lib.q8k_flash_attention_multi_out
+        check(fn(ptr(q), ptr(k), ptr(v), ctypes.cast(outs, ctypes.c_void_p), len(dest_ptrs), dt(out_type), B, h, M, N,
+                 *strides, float(softmax_scale), ptr(batch_mask), ptr(_lib.status_word(dev)), stream_ptr(dev)),
               "flash_attention")
 
 
@@ -558,6 +570,22 @@ def attention_prep_v(v: torch.Tensor) -> torch.Tensor:
         check(lib.q8k_attention_prep_v(ptr(v), ptr(vt8), B, H, S, v.stride(0), v.stride(2), v.stride(1), stream_ptr(dev)),
               "attention_prep_v")
     return vt8
+
+
+def attention_cast_rows(v: torch.Tensor) -> torch.Tensor:
+    """bf16 [B,H,S,64] view -> e4m3 [B,H,S,64] contiguous (the unscaled ``.to(float8_e4m3fn)`` the
+    reference applies to V, q8_kernels/functional/flash_attention.py:47-48), for ``flash_attention(v_rows=True)``."""
+    dev = require_cuda(v)
+    B, H, S, D = v.shape
+    if D != 64 or v.dtype != torch.bfloat16:
+        raise Q8KernelError("attention_cast_rows: v must be bfloat16 with head dim 64")
+    if v.stride(3) != 1 or any(s % 8 for s in v.stride()[:3]) or v.data_ptr() % 16:
+        v = v.contiguous()
+    out = torch.empty((B, H, S, 64), dtype=E4M3, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_attention_cast_rows(ptr(v), ptr(out), B, H, S, v.stride(0), v.stride(2), v.stride(1),
+                                          stream_ptr(dev)), "attention_cast_rows")
+    return out
 
 
 # ---------------------------------------------------------------- fused linear chain

@@ -305,3 +305,24 @@ def test_abandoned_wait_is_reported_and_the_context_survives(nat, cuda_device):
     del skipped
     again = nat.flash_attention(q8, k8, vt, ks, None, torch.bfloat16)
     assert torch.equal(again, want)
+
+
+@pytest.mark.parametrize("B,H,M,N,lens", [(1, 2, 256, 320, None), (2, 3, 130, 1025, None), (2, 4, 384, 128, [65, 127]),
+                                          (1, 1, 100, 77, None), (2, 2, 200, 128, [0, 100])])
+def test_v_as_rows_gives_the_same_bits_as_v_transposed(nat, cuda_device, B, H, M, N, lens):
+    """V handed over as [B,H,N,64] rows and read MN-major by the tensor core against the reference's
+    transposed, padded layout: the same products in the same order, so identical outputs."""
+    d = cuda_device
+    q8, k8, vt, ks = _fp8_operands(B, H, M, N, seed=M + 3 * N)
+    v_rows = vt[..., :N].transpose(2, 3).contiguous()
+    mask = None if lens is None else torch.tensor(lens, dtype=torch.int32, device=d)
+    a = nat.flash_attention(q8.to(d), k8.to(d), vt.to(d), ks, mask, torch.bfloat16)
+    b = nat.flash_attention(q8.to(d), k8.to(d), v_rows.to(d), ks, mask, torch.bfloat16, v_rows=True)
+    assert torch.equal(a, b)
+
+
+def test_attention_cast_rows_is_the_unscaled_e4m3_cast(nat, cuda_device):
+    _, _, v = Hp.qkv(2, 3, 77, 64, seed=9)                   # [B,H,S,64] view of [B,S,H*64]
+    got = nat.attention_cast_rows(v.to(cuda_device))
+    assert got.shape == (2, 3, 77, 64) and got.is_contiguous()
+    Hp.assert_bit_equal(got, O.c10_e4m3(v).contiguous(), "v rows")
