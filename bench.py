@@ -509,7 +509,7 @@ def detail_head_sharded_block(q8, dev, rank, world):
     """One DiT block on 6144 tokens with the self- and cross-attention cores sharded by head over the
     ranks (H / world heads each); linears, norms and RoPE replicated.  Two ways to reassemble the
     channel dim before the output projection: an NCCL all-gather, or the attention kernel storing its
-    heads into every rank's buffer (used up to the world size that path has been verified for).  Every
+    heads into every rank's buffer (up to the 8 destinations one launch can store to).  Every
     variant is compared bit for bit with the replicated block.  Max over ranks of the CUDA-event time."""
     import torch.distributed as dist
     from q8_kernels_b200 import sharding
@@ -572,6 +572,10 @@ def run_case(a):
         mm, mmb = (nat.fp8_mm, nat.fp8_mm_bias) if qd == E4M3 else (nat.q8_mm, nat.q8_mm_bias)
         fn = (lambda: mmb(xq, wq, bias, xs, ws, True, torch.bfloat16)) if a.gelu else \
              (lambda: mm(xq, wq, xs, ws, False, torch.bfloat16))
+        if a.resid:                                       # the block's "gate * linear + residual" epilogue
+            gate = torch.randn(1, 1, a.n, generator=g, device=dev).to(torch.bfloat16)
+            resid = torch.randn(1, a.m, a.n, generator=g, device=dev).to(torch.bfloat16)
+            fn = lambda: nat.mm_gate_residual(xq, wq, bias, xs, ws, gate, resid)                       # noqa: E731
         work = 2.0 * a.m * a.k * a.n / 1e12
     elif a.case in ("attention", "cross_attention", "qk_prep", "prep_v"):
         skv = a.skv if a.skv > 0 else (a.s if a.case != "cross_attention" else 128)
@@ -655,6 +659,7 @@ def main():
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--n", type=int, default=2048)
     ap.add_argument("--gelu", action="store_true", help="GEMM case with bias + tanh-GELU epilogue")
+    ap.add_argument("--resid", action="store_true", help="GEMM case with the gate * y + residual epilogue")
     ap.add_argument("--b", type=int, default=1)
     ap.add_argument("--h", type=int, default=8)
     ap.add_argument("--s", type=int, default=4096)

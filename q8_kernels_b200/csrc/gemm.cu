@@ -287,6 +287,13 @@ gemm_8bit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 
     // ---------------------------------------------------- teardown
+    if (threadIdx.x == 0 && *abort_flag != 0) {
+        // A wait was abandoned.  Copies issued before that may still be on their way into this CTA's
+        // shared memory and towards its barriers: give them time to land (they take microseconds)
+        // before the CTA gives both up.
+        const unsigned long long t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 50000ull) {}
+    }
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == 1) {

@@ -26,25 +26,33 @@
 namespace q8k {
 
 constexpr int kPairBN = 256;                 // tile columns (128 B rows from each CTA)
-constexpr int kPairStages = 6;
 constexpr int kPairTmemCols = 512;           // two 256-column accumulators per CTA
 
-struct PairSmem {
+// Shared memory of one CTA.  The gate/residual variant gives one of the six pipeline stages to residual
+// staging: per epilogue warp two 32-row boxes that TMA fills one and two chunks ahead of their use.
+template <bool RESID>
+struct PairSmemT {
+    static constexpr int kStages = RESID ? 5 : 6;
     static constexpr int kABytes = kGemmBM * kGemmBK;              // 16 KB: this CTA's 128 rows of A
     static constexpr int kBBytes = (kPairBN / 2) * kGemmBK;        // 16 KB: this CTA's 128 rows of B
     static constexpr int kStageBytes = kABytes + kBBytes;
     // output staging: per epilogue warp two 32-row boxes of 64 bytes per row (bf16) or 32 (e4m3)
     static constexpr int kStoreBoxBytes = 32 * 64;
-    static constexpr int kStoreOffset = kPairStages * kStageBytes;
+    static constexpr int kStoreOffset = kStages * kStageBytes;
     static constexpr int kStoreBytes = (kGemmEpilogueThreads / 32) * 2 * kStoreBoxBytes;
-    static constexpr int kBarOffset = kStoreOffset + kStoreBytes;
-    static constexpr int kNumBars = 2 * kPairStages + 4;
+    // residual staging (bf16 rows of 64 bytes), same box shape and swizzle as the output boxes
+    static constexpr int kResidOffset = kStoreOffset + kStoreBytes;
+    static constexpr int kResidBytes = RESID ? (kGemmEpilogueThreads / 32) * 2 * kStoreBoxBytes : 0;
+    static constexpr int kBarOffset = kResidOffset + kResidBytes;
+    static constexpr int kNumResidBars = RESID ? (kGemmEpilogueThreads / 32) * 2 : 0;
+    static constexpr int kNumBars = 2 * kStages + 4 + kNumResidBars;
     static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
     static constexpr int kAbortOffset = kTmemPtrOffset + 4;
     static constexpr int kPriorOffset = kAbortOffset + 4;
     static constexpr int kColScaleOffset = (kPriorOffset + 4 + 15) & ~15;
     static constexpr int kBiasOffset = kColScaleOffset + kPairBN * 4;
-    static constexpr int kTotal = kBiasOffset + kPairBN * 4;
+    static constexpr int kGateOffset = kBiasOffset + kPairBN * 4;  // bf16 gate row of the tile (gate/residual epilogue)
+    static constexpr int kTotal = kGateOffset + kPairBN * 2;
     // No alignment slack: the kernel has no static shared memory, so the dynamic window starts on
     // a 1024-byte boundary; the kernel checks that and reports instead of running misaligned.
     static constexpr int kDynamic = kTotal;
@@ -62,8 +70,10 @@ struct PairParams {
 template <bool INT8, bool GELU, bool OUT_E4M3, bool RESID>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_c, const PairParams pp) {
-    using L = PairSmem;
+                      const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
+                      const PairParams pp) {
+    using L = PairSmemT<RESID>;
+    constexpr int kPairStages = L::kStages;
     const GemmParams& p = pp.g;
     constexpr uint32_t IDESC = INT8 ? ptx::make_idesc_s8(2 * kGemmBM, kPairBN) : ptx::make_idesc_e4m3(2 * kGemmBM, kPairBN);
 
@@ -78,10 +88,12 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
     auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + a); };
     auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + 2 + a); };
+    auto resid_bar = [&](int w, int i) { return bar_base + 8u * (2 * kPairStages + 4 + 2 * w + i); };   // RESID only
     volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
     float* col_scale_smem = reinterpret_cast<float*>(smem + L::kColScaleOffset);
     float* bias_smem = reinterpret_cast<float*>(smem + L::kBiasOffset);
+    __nv_bfloat16* gate_smem = reinterpret_cast<__nv_bfloat16*>(smem + L::kGateOffset);
 
     const uint32_t rank = ptx::cluster_ctarank();              // 0 = leader, 1 = peer
     const bool leader = rank == 0;
@@ -113,12 +125,19 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             ptx::mbar_init(tmem_full_bar(a), 1);
             ptx::mbar_init(tmem_empty_bar(a), 2 * (kGemmEpilogueThreads / 32));   // every epilogue warp of both CTAs
         }
+        if constexpr (RESID) {
+            for (int w = 0; w < kGemmEpilogueThreads / 32; ++w) {
+                ptx::mbar_init(resid_bar(w, 0), 1);
+                ptx::mbar_init(resid_bar(w, 1), 1);
+            }
+        }
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
         if (pp.tma_store) ptx::prefetch_tensormap(&tmap_c);
+        if (RESID && pp.tma_store) ptx::prefetch_tensormap(&tmap_r);
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair<kPairTmemCols>(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)));
@@ -206,6 +225,8 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const uint32_t store_base = smem_base + L::kStoreOffset + (uint32_t)(warp - 2) * 2u * L::kStoreBoxBytes;
         uint32_t tile_i = 0;
         uint32_t store_i = 0;                                  // stores issued by this warp: picks the staging box
+        uint32_t resid_i = 0, resid_c = 0;                     // residual boxes requested (lane 0) / consumed by this warp
+        const uint32_t resid_base = smem_base + L::kResidOffset + (uint32_t)(warp - 2) * 2u * L::kStoreBoxBytes;
         bool ok = true;
         for (int tile = cluster_id; tile < pp.total_tiles2; tile += num_clusters, ++tile_i) {
             const int n_blk = tile % pp.n_tiles2;
@@ -215,19 +236,21 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             const uint32_t acc = tile_i & 1u;
             const uint32_t acc_ph = (tile_i >> 1) & 1u;
 
+            // gate row of this CTA's first row: the whole tile's, unless the tile straddles two gate rows
+            int64_t gate_row_tile = 0;
+            if constexpr (RESID)
+                gate_row_tile = (((int64_t)batch * p.M + m_blk * 2 * kGemmBM + (int)rank * kGemmBM) / p.rows_per_gate) * p.N;
             asm volatile("bar.sync 1, 256;" ::: "memory");
             for (int c = epi_tid; c < kPairBN; c += kGemmEpilogueThreads) {
                 const int n = n0 + c;
                 const bool in = n < p.N;
                 col_scale_smem[c] = in ? p.b_scales[(p.batch_b ? (int64_t)batch * p.N : 0) + n] : 0.f;
                 bias_smem[c] = (in && p.bias != nullptr) ? p.bias[n] : 0.f;
+                if constexpr (RESID) {
+                    if (p.gate != nullptr) gate_smem[c] = in ? p.gate[gate_row_tile + n] : __float2bfloat16(0.f);
+                }
             }
             asm volatile("bar.sync 1, 256;" ::: "memory");
-
-            if (ok) ok = ptx::mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) continue;
-            ptx::tcgen05_fence_after_sync();
 
             const int row = m_blk * 2 * kGemmBM + (int)rank * kGemmBM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
@@ -236,6 +259,32 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             const int64_t gate_row = RESID ? (((int64_t)batch * p.M + row) / p.rows_per_gate) * p.N : 0;
             const int col_base = half * HALF_COLS;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kPairBN + col_base;
+
+            // Residual of this warp's 32 rows, one 32-column chunk per box (staged bf16 path): TMA loads it
+            // into the warp's two residual boxes, the first two chunks before the accumulator is even
+            // complete and chunk c+2 as soon as chunk c has been read out, so that the latency of the
+            // residual is not paid inside the chunk that uses it.
+            auto issue_resid = [&](int c) {                     // lane 0; chunks with columns inside N only
+                const int nc = n0 + col_base + c * 32;
+                if (nc < p.N) {
+                    const uint32_t rb = resid_bar(warp - 2, (int)(resid_i & 1u));
+                    ptx::mbar_arrive_expect_tx(rb, L::kStoreBoxBytes);
+                    ptx::tma_load_3d(resid_base + (resid_i & 1u) * L::kStoreBoxBytes, &tmap_r, rb, nc * 2,
+                                     m_blk * 2 * kGemmBM + (int)rank * kGemmBM + quarter * 32, batch);
+                    ++resid_i;
+                }
+            };
+            if constexpr (RESID && !OUT_E4M3) {
+                if (staged && lane == 0) {
+                    issue_resid(0);
+                    issue_resid(1);
+                }
+            }
+
+            if (ok) ok = ptx::mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) continue;
+            ptx::tcgen05_fence_after_sync();
 
             uint32_t r[2][32];
             __syncwarp();
@@ -246,6 +295,28 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 if (c + 1 < NCH) ptx::tmem_ld_32x32b_x32(t_row + (c + 1) * 32, r[(c + 1) & 1]);
                 const int cl = col_base + c * 32;
                 const int nc = n0 + cl;
+                uint32_t rs_cur[16];
+                if constexpr (RESID && !OUT_E4M3) {
+                    if (staged && nc < p.N) {                  // warp-uniform
+                        // this thread's row of the residual box (same swizzle as the output box)
+                        const uint32_t rbox = resid_base + (resid_c & 1u) * L::kStoreBoxBytes;
+                        if (!ptx::mbar_wait(resid_bar(warp - 2, (int)(resid_c & 1u)), (resid_c >> 1) & 1u, abort_flag)) ok = false;
+                        ++resid_c;
+                        const uint32_t rrow = rbox + (uint32_t)lane * 64u;
+                        const uint32_t rsw = ((uint32_t)lane >> 1) & 3u;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(rs_cur[4 * q]), "=r"(rs_cur[4 * q + 1]), "=r"(rs_cur[4 * q + 2]), "=r"(rs_cur[4 * q + 3])
+                                         : "r"(rrow + (((uint32_t)q ^ rsw) << 4))
+                                         : "memory");
+                        __syncwarp();
+                        if (lane == 0 && c + 2 < NCH) {
+                            ptx::fence_proxy_async_smem();
+                            issue_resid(c + 2);
+                        }
+                    }
+                }
                 if (staged) {
                     if (nc < p.N) {                            // warp-uniform
                         const uint32_t(&rc)[32] = r[c & 1];
@@ -275,11 +346,11 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                            ((uint32_t)float2_to_e4m3x2_sat(y1.x, y1.y) << 16);
                                 }
                             } else {
-                                uint4 rs = make_uint4(0, 0, 0, 0), gt = make_uint4(0, 0, 0, 0);
+                                uint4 gt = make_uint4(0, 0, 0, 0);
                                 if constexpr (RESID) {
-                                    if (row_ok && nc + q * 8 < p.N) {
-                                        rs = *reinterpret_cast<const uint4*>(p.resid + out_row + nc + q * 8);
-                                        if (p.gate != nullptr)
+                                    if (p.gate != nullptr) {
+                                        if (gate_row == gate_row_tile) gt = *reinterpret_cast<const uint4*>(gate_smem + cl + q * 8);
+                                        else if (row_ok && nc + q * 8 < p.N)
                                             gt = *reinterpret_cast<const uint4*>(p.gate + gate_row + nc + q * 8);
                                     }
                                 }
@@ -290,16 +361,16 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                                                                 bias_smem + cl + j);
                                     __nv_bfloat162 b2 = __floats2bfloat162_rn(y0.x, y0.y);
                                     if constexpr (RESID) {
-                                        // out = bf16(bf16(gate * bf16(y)) + resid), the roundings of the separate torch ops
-                                        float2 f = __bfloat1622float2(b2);
+                                        // out = bf16(bf16(gate * bf16(y)) + resid), the roundings of the separate torch
+                                        // ops.  Packed bf16 arithmetic gives exactly those: a product of two bf16 values
+                                        // is exact in fp32, and a sum of two is either exact in fp32 or so lopsided that
+                                        // both roundings return the larger operand; _rn keeps the two from fusing.
                                         if (p.gate != nullptr) {
-                                            const uint32_t gw = (&gt.x)[e];
-                                            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw));
-                                            f = __bfloat1622float2(__floats2bfloat162_rn(g.x * f.x, g.y * f.y));
+                                            const uint32_t gw = e == 0 ? gt.x : (e == 1 ? gt.y : (e == 2 ? gt.z : gt.w));
+                                            b2 = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&gw), b2);
                                         }
-                                        const uint32_t rw = (&rs.x)[e];
-                                        const float2 r2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw));
-                                        b2 = __floats2bfloat162_rn(f.x + r2.x, f.y + r2.y);
+                                        const uint32_t rw = rs_cur[4 * q + e];
+                                        b2 = __hadd2_rn(b2, *reinterpret_cast<const __nv_bfloat162*>(&rw));
                                     }
                                     w[e] = *reinterpret_cast<uint32_t*>(&b2);
                                 }
@@ -390,6 +461,13 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
     // ---------------------------------------------------- teardown: neither CTA may leave while the other can
     // still read its shared memory, signal its barriers or write its TMEM
+    if (threadIdx.x == 0 && *abort_flag != 0) {
+        // A wait was abandoned.  Copies issued before that may still be on their way into this CTA's
+        // shared memory and towards its barriers: give them time to land (they take microseconds)
+        // before the CTA gives both up.
+        const unsigned long long t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 50000ull) {}
+    }
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
     ptx::cluster_sync_all();
@@ -401,8 +479,9 @@ gemm_8bit_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
 // ------------------------------------------------------------------ host side
 template <bool INT8, bool GELU, bool OUT_E4M3, bool RESID = false>
-static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const PairParams& pp,
-                       cudaStream_t st) {
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tr,
+                       const PairParams& pp, cudaStream_t st) {
+    using PairSmem = PairSmemT<RESID>;
     auto kern = gemm_8bit_pair_kernel<INT8, GELU, OUT_E4M3, RESID>;
     Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamic));
     // how many 2-CTA clusters can be resident at once (cached per kernel variant)
@@ -423,7 +502,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     }
     if (max_clusters < 8) return Q8K_ERR_UNSUPPORTED;
     const int clusters = pp.total_tiles2 < max_clusters ? pp.total_tiles2 : max_clusters;
-    kern<<<2 * clusters, kGemmThreads, PairSmem::kDynamic, st>>>(ta, tb, tc, pp);
+    kern<<<2 * clusters, kGemmThreads, PairSmem::kDynamic, st>>>(ta, tb, tc, tr, pp);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }
@@ -448,7 +527,7 @@ int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, bool resid, const void
     pp.g = p;
     const int batch = bs_a > bs_b ? bs_a : bs_b;
     // output map for the staged epilogue: [batch, M, N] as bytes, 32-column boxes of 32 rows
-    CUtensorMap tc = ta;
+    CUtensorMap tc = ta, tr = ta;
     const uint64_t esz = out_e4m3 ? 1 : 2;
     pp.tma_store = 0;
     if (((uint64_t)p.N * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
@@ -457,6 +536,11 @@ int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, bool resid, const void
         const uint32_t box[3] = {(uint32_t)(32 * esz), 32u, 1u};
         if (int rc = make_byte_tensor_map(&tc, p.out, 3, dims, strides, box, (int)(32 * esz), op)) return rc;
         pp.tma_store = 1;
+        // the residual has the output's shape: same boxes, read instead of written
+        if (resid) {
+            if ((reinterpret_cast<uintptr_t>(p.resid) & 15) != 0) pp.tma_store = 0;
+            else if (int rc = make_byte_tensor_map(&tr, p.resid, 3, dims, strides, box, (int)(32 * esz), op)) return rc;
+        }
     }
     pp.m_tiles2 = (p.M + 2 * kGemmBM - 1) / (2 * kGemmBM);
     pp.n_tiles2 = (p.N + kPairBN - 1) / kPairBN;
@@ -465,14 +549,14 @@ int launch_gemm_pair(bool int8, bool gelu, bool out_e4m3, bool resid, const void
     pp.total_tiles2 = (int)total;
 #define Q8K_PAIR(I8)                                                                  \
     do {                                                                              \
-        if (gelu) return out_e4m3 ? launch_pair<I8, true, true>(ta, tb, tc, pp, st)       \
-                                  : launch_pair<I8, true, false>(ta, tb, tc, pp, st);     \
-        return out_e4m3 ? launch_pair<I8, false, true>(ta, tb, tc, pp, st)                \
-                        : launch_pair<I8, false, false>(ta, tb, tc, pp, st);              \
+        if (gelu) return out_e4m3 ? launch_pair<I8, true, true>(ta, tb, tc, tr, pp, st)       \
+                                  : launch_pair<I8, true, false>(ta, tb, tc, tr, pp, st);     \
+        return out_e4m3 ? launch_pair<I8, false, true>(ta, tb, tc, tr, pp, st)                \
+                        : launch_pair<I8, false, false>(ta, tb, tc, tr, pp, st);              \
     } while (0)
     if (resid) {
-        return int8 ? launch_pair<true, false, false, true>(ta, tb, tc, pp, st)
-                    : launch_pair<false, false, false, true>(ta, tb, tc, pp, st);
+        return int8 ? launch_pair<true, false, false, true>(ta, tb, tc, tr, pp, st)
+                    : launch_pair<false, false, false, true>(ta, tb, tc, tr, pp, st);
     }
     if (int8) Q8K_PAIR(true);
     Q8K_PAIR(false);
