@@ -61,9 +61,10 @@ struct AttnSmem {
     static constexpr int kKOff = kQOff + kQBytes;
     static constexpr int kVOff = kKOff + kAttnKS * kKBytes;
     static constexpr int kPOff = kVOff + kAttnKS * kVBytes;
-    static constexpr int kBarOff = kPOff + 2 * kPBytes;
-    // q_full, k_full[3], v_full[3], slot_free, s_full, step_end
-    static constexpr int kNumBars = 1 + 2 * kAttnKS + 3;
+    static constexpr int kQ2Off = kPOff + 2 * kPBytes;             // second Q buffer (several query tiles per CTA)
+    static constexpr int kBarOff = kQ2Off + kQBytes;
+    // q_full[2], k_full[3], v_full[3], slot_free, s_full, step_end, q_free[2]
+    static constexpr int kNumBars = 2 + 2 * kAttnKS + 3 + 2;
     static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemPtrOff + 4;
     static constexpr int kTotal = kAbortOff + 4;
@@ -80,6 +81,7 @@ struct AttnParams {
     int B, H, M, N;
     float scale_log2;                      // softmax_scale * log2(e)
     int out_e4m3;
+    int tma_out;                           // 1: one destination, stored through tmap_o; 2: same, rows before heads in the map
     int64_t out_stride_b, out_stride_h, out_stride_s;   // output strides in elements (head dim contiguous)
 };
 
@@ -125,21 +127,31 @@ __device__ __forceinline__ void bounded_wait(uint32_t bar, uint32_t parity, uint
 // V_ROWS = false: V arrives transposed, [B,H,64,ceil16(N)] (the reference's layout), and is the K-major B
 // operand of P.V.  V_ROWS = true: V arrives as rows, [B,H,N,64] like K, is loaded by the same kind of TMA
 // box and read by the tensor core as an MN-major B operand, so no transpose pass is needed.
-template <bool V_ROWS>
+// MULTI = true (short key sequences, at most kAttnKS blocks: cross-attention): a CTA keeps K and V of its
+// (batch, head) in shared memory and walks over several query tiles (blockIdx.x, + gridDim.x, ...), so that
+// barrier set-up, TMEM allocation and the K/V loads are paid once per CTA instead of once per 128 rows.
+template <bool V_ROWS, bool MULTI>
 __global__ void __maxnreg__(kAttnRegsLaunch)
 flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-               const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+               const AttnParams p) {
     using L = AttnSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t smem_base = ptx::smem_u32(smem);
     const uint32_t bar_base = smem_base + L::kBarOff;
-    const uint32_t q_full = bar_base;
-    auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
-    auto v_full = [&](int s) { return bar_base + 8u * (1 + kAttnKS + s); };
-    const uint32_t slot_free = bar_base + 8u * (1 + 2 * kAttnKS);   // P.V(i) and Q.K^T(i+2) retired       (phase i)
-    const uint32_t s_full = slot_free + 8u;                         // see the MMA issuer                  (phase k)
-    const uint32_t step_end = slot_free + 16u;                      // softmax: prologue (phase 0), step i (phase i+1)
+    auto q_full = [&](int i) { return bar_base + 8u * i; };
+    auto k_full = [&](int s) { return bar_base + 8u * (2 + s); };
+    auto v_full = [&](int s) { return bar_base + 8u * (2 + kAttnKS + s); };
+    // The three below complete their phases in a fixed order (per query tile: slot_free nblk, s_full nblk + 2,
+    // step_end nblk + 1, or nblk + 2 with MULTI) and every waiter consumes them in that order.  No barrier can
+    // be more than one completed phase ahead of a thread that still has to wait on it: the protocol makes
+    // every producer depend on that waiter before it can complete a second one.
+    const uint32_t slot_free = bar_base + 8u * (2 + 2 * kAttnKS);   // P.V(i) and Q.K^T(i+2) retired
+    const uint32_t s_full = slot_free + 8u;                         // see the MMA issuer
+    const uint32_t step_end = slot_free + 16u;                      // softmax: prologue, one per step, (MULTI) epilogue reached
+    auto q_free = [&](int i) { return slot_free + 24u + 8u * i; };  // MULTI: all tensor-core reads of Q buffer i retired
+    auto q_off = [&](int i) { return (uint32_t)(i ? L::kQ2Off : L::kQOff); };
     volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
     const uint32_t abort_addr = smem_base + L::kAbortOff;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
@@ -152,8 +164,11 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int bh = blockIdx.y;
-    const int m0 = blockIdx.x * kAttnBM;
     const int b = bh / p.H;
+    // query tiles of this CTA: tile0, tile0 + tstride, ... (one tile unless MULTI)
+    const int tile0 = blockIdx.x;
+    const int tstride = MULTI ? (int)gridDim.x : 1;
+    const int n_tiles = MULTI ? ((p.M + kAttnBM - 1) / kAttnBM - tile0 + tstride - 1) / tstride : 1;
 
     int valid = p.N;
     bool all_masked = false;
@@ -166,7 +181,8 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int nblk = (k_range + kAttnBN - 1) / kAttnBN;          // >= 1
 
     if (threadIdx.x == 0) {
-        ptx::mbar_init(q_full, 1);
+        ptx::mbar_init(q_full(0), 1);
+        ptx::mbar_init(q_full(1), 1);
         for (int s = 0; s < kAttnKS; ++s) {
             ptx::mbar_init(k_full(s), 1);
             ptx::mbar_init(v_full(s), 1);
@@ -174,12 +190,15 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         ptx::mbar_init(slot_free, 1);
         ptx::mbar_init(s_full, 1);
         ptx::mbar_init(step_end, 4);
+        ptx::mbar_init(q_free(0), 1);
+        ptx::mbar_init(q_free(1), 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
         ptx::prefetch_tensormap(&tmap_q);
         ptx::prefetch_tensormap(&tmap_k);
         ptx::prefetch_tensormap(&tmap_v);
+        if (p.tma_out) ptx::prefetch_tensormap(&tmap_o);
     }
     if (warp == 1) {
         ptx::tmem_alloc<kAttnTmemCols>(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)));
@@ -199,8 +218,11 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (warp == 0) {
             // -------------------------------------------- TMA producer
             if (lane == 0) {
-                ptx::mbar_arrive_expect_tx(q_full, L::kQBytes);
-                ptx::tma_load_3d(smem_base + L::kQOff, &tmap_q, q_full, 0, m0, bh);
+                auto load_q = [&](int t) {                      // query tile t of this CTA into Q buffer t & 1
+                    ptx::mbar_arrive_expect_tx(q_full(t & 1), L::kQBytes);
+                    ptx::tma_load_3d(smem_base + q_off(t & 1), &tmap_q, q_full(t & 1), 0, (tile0 + t * tstride) * kAttnBM, bh);
+                };
+                load_q(0);
                 auto load_kv = [&](int j) {                     // block j (visit order) into slot j % 3
                     const int jb = nblk - 1 - j;
                     const int s = j % kAttnKS;
@@ -212,11 +234,22 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 };
                 const int first = nblk < kAttnKS ? nblk : kAttnKS;
                 for (int j = 0; j < first; ++j) load_kv(j);
-                for (int i = 0; i + kAttnKS < nblk; ++i) {
-                    // K(i) was consumed before step i, V(i) by P.V(i): both slots i % 3 are free
-                    bounded_wait(slot_free, (uint32_t)i & 1u, abort_addr, 4);
-                    if (*abort_flag != 0) break;                // a wait was abandoned: issue nothing more
-                    load_kv(i + kAttnKS);
+                if constexpr (MULTI) {
+                    // K and V stay where they are (nblk <= kAttnKS).  Q(t+2) goes into the buffer of tile t
+                    // once all tensor-core work of tile t has retired.
+                    if (n_tiles > 1) load_q(1);
+                    for (int t = 0; t + 2 < n_tiles; ++t) {
+                        bounded_wait(q_free(t & 1), (uint32_t)(t >> 1) & 1u, abort_addr, 4);
+                        if (*abort_flag != 0) break;
+                        load_q(t + 2);
+                    }
+                } else {
+                    for (int i = 0; i + kAttnKS < nblk; ++i) {
+                        // K(i) was consumed before step i, V(i) by P.V(i): both slots i % 3 are free
+                        bounded_wait(slot_free, (uint32_t)i & 1u, abort_addr, 4);
+                        if (*abort_flag != 0) break;            // a wait was abandoned: issue nothing more
+                        load_kv(i + kAttnKS);
+                    }
                 }
                 // (slot_free phases that are never waited on simply complete.)
                 if (*abort_flag != 0) {
@@ -232,41 +265,48 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 // P.V with V as rows: B operand MN-major (bit 16); its 32-key K slices are 32 rows of 64 bytes apart
                 constexpr uint32_t IDESC_PV = V_ROWS ? (IDESC | (1u << 16)) : IDESC;
                 constexpr uint32_t V_KSTEP = V_ROWS ? (32 * 64) >> 4 : 2;
-                const uint64_t q_desc = ptx::make_kmajor_desc(smem_base + L::kQOff, 64);
                 const uint32_t s_tmem = tmem_base;
                 const uint32_t o_tmem = tmem_base + kAttnOCol;
-                auto issue_qk = [&](int j) {
-                    const int s = j % kAttnKS;
-                    bounded_wait(k_full(s), (uint32_t)(j / kAttnKS) & 1u, abort_addr, 5);
-                    ptx::tcgen05_fence_after_sync();
-                    const uint64_t k_desc = ptx::make_kmajor_desc(smem_base + L::kKOff + s * L::kKBytes, 64);
-#pragma unroll
-                    for (int k = 0; k < kAttnD / 32; ++k)
-                        ptx::mma_f8f6f4(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC, k > 0 ? 1u : 0u);
-                };
-                // s_full phases: 0 = Q.K^T(0); 1 = Q.K^T(1) (if any); i+2 = P.V(i) and Q.K^T(i+2) (if any).
-                // So phase i+1, which the softmax warps wait for in the middle of step i, says that the
-                // scores of block i+1 are in TMEM AND (i >= 1) that O holds P.V up to block i-1; phase
+                // s_full phases of one tile: 0 = Q.K^T(0); 1 = Q.K^T(1) (if any); i+2 = P.V(i) and Q.K^T(i+2)
+                // (if any).  So phase i+1, which the softmax warps wait for in the middle of step i, says that
+                // the scores of block i+1 are in TMEM AND (i >= 1) that O holds P.V up to block i-1; phase
                 // nblk+1 says that O is complete.
-                bounded_wait(q_full, 0, abort_addr, 5);
-                issue_qk(0);
-                ptx::tcgen05_commit(s_full);
-                bounded_wait(step_end, 0, abort_addr, 5);        // S(0) is in registers
-                if (nblk > 1) issue_qk(1);
-                ptx::tcgen05_commit(s_full);
-                for (int i = 0; i < nblk; ++i) {
-                    const int s = i % kAttnKS;
-                    bounded_wait(step_end, (uint32_t)(i + 1) & 1u, abort_addr, 5);   // P(i) written, O rescaled, S free
-                    bounded_wait(v_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_addr, 5);
-                    ptx::tcgen05_fence_after_sync();
-                    const uint64_t p_desc = ptx::make_kmajor_desc(smem_base + L::kPOff + (i & 1) * L::kPBytes, 64);
-                    const uint64_t v_desc = ptx::make_kmajor_desc(smem_base + L::kVOff + s * L::kVBytes, 64);
+                for (int t = 0; t < n_tiles; ++t) {
+                    const uint32_t e_base = MULTI ? (uint32_t)t * (uint32_t)(nblk + 2) : 0u;   // step_end phases of earlier tiles
+                    // The softmax warps must have seen the last s_full phase of the tile before (they then
+                    // arrive once more) before this tile completes another one.
+                    if (MULTI && t > 0) bounded_wait(step_end, (e_base - 1u) & 1u, abort_addr, 5);
+                    const uint64_t q_desc = ptx::make_kmajor_desc(smem_base + q_off(t & 1), 64);
+                    auto issue_qk = [&](int j) {
+                        const int s = j % kAttnKS;
+                        bounded_wait(k_full(s), (uint32_t)(j / kAttnKS) & 1u, abort_addr, 5);
+                        ptx::tcgen05_fence_after_sync();
+                        const uint64_t k_desc = ptx::make_kmajor_desc(smem_base + L::kKOff + s * L::kKBytes, 64);
 #pragma unroll
-                    for (int k = 0; k < kAttnBN / 32; ++k)
-                        ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + V_KSTEP * k, IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
-                    if (i + 2 < nblk) issue_qk(i + 2);
+                        for (int k = 0; k < kAttnD / 32; ++k)
+                            ptx::mma_f8f6f4(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC, k > 0 ? 1u : 0u);
+                    };
+                    bounded_wait(q_full(t & 1), (uint32_t)(t >> 1) & 1u, abort_addr, 5);
+                    issue_qk(0);                                 // (the score tile is free: S(last) of the tile before
+                    ptx::tcgen05_commit(s_full);                 //  went to registers before its last step ended)
+                    bounded_wait(step_end, e_base & 1u, abort_addr, 5);          // S(0) is in registers
+                    if (nblk > 1) issue_qk(1);
                     ptx::tcgen05_commit(s_full);
-                    ptx::tcgen05_commit(slot_free);
+                    for (int i = 0; i < nblk; ++i) {
+                        const int s = i % kAttnKS;
+                        bounded_wait(step_end, (e_base + (uint32_t)i + 1u) & 1u, abort_addr, 5);   // P(i) written, O rescaled, S free
+                        bounded_wait(v_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_addr, 5);
+                        ptx::tcgen05_fence_after_sync();
+                        const uint64_t p_desc = ptx::make_kmajor_desc(smem_base + L::kPOff + (i & 1) * L::kPBytes, 64);
+                        const uint64_t v_desc = ptx::make_kmajor_desc(smem_base + L::kVOff + s * L::kVBytes, 64);
+#pragma unroll
+                        for (int k = 0; k < kAttnBN / 32; ++k)
+                            ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + V_KSTEP * k, IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
+                        if (i + 2 < nblk) issue_qk(i + 2);
+                        ptx::tcgen05_commit(s_full);
+                        ptx::tcgen05_commit(slot_free);
+                    }
+                    if (MULTI) ptx::tcgen05_commit(q_free(t & 1));
                 }
             }
         }
@@ -281,18 +321,21 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         // ------------------------------------------------ softmax / O rescale / epilogue
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
-        const int row = m0 + r;
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const float c = p.scale_log2;
         const uint32_t swz = (uint32_t)((r >> 1) & 3);
         // this row's 16-byte chunk ch of P buffer 0 sits at p_a0 ^ (ch << 4) (64B swizzle; the row starts 64-byte aligned)
         const uint32_t p_a0 = (smem_base + L::kPOff + (uint32_t)r * kAttnBN) | (swz << 4);
 
+        uint32_t cur[2][32];
+#pragma unroll 1
+        for (int t = 0; t < n_tiles; ++t) {
+        const int row = (tile0 + t * tstride) * kAttnBM + r;
+        const uint32_t s_base = MULTI ? (uint32_t)t * (uint32_t)(nblk + 2) : 0u;   // s_full phases of earlier tiles
         float m_run = -INFINITY;
         float l_run = 0.f;
-        uint32_t cur[2][32];
 
-        bounded_wait(s_full, 0, abort_addr, 6);
+        bounded_wait(s_full, s_base & 1u, abort_addr, 6);
         ptx::tcgen05_fence_after_sync();
         ptx::tmem_ld_32x32b_x32(t_lane, cur[0]);
         ptx::tmem_ld_32x32b_x32(t_lane + 32, cur[1]);
@@ -300,6 +343,12 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         ptx::tcgen05_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(step_end);
+
+        // the output boxes of the tile before sit in this warp's P rows until TMA has read them out
+        if (MULTI && t > 0 && p.tma_out) {
+            if (lane == 0) ptx::bulk_wait_group_read<0>();
+            __syncwarp();
+        }
 
         // columns >= N get -inf, columns >= key_lens[b] the reference's mask value
         auto mask_scores = [&](int i) {
@@ -365,7 +414,7 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 }
                 if (h == 0) {
                     // scores of block i+1 are in TMEM; for i >= 1 also: P.V(i-1) has retired
-                    bounded_wait(s_full, (uint32_t)(i + 1) & 1u, abort_addr, 6);
+                    bounded_wait(s_full, (s_base + (uint32_t)i + 1u) & 1u, abort_addr, 6);
                     ptx::tcgen05_fence_after_sync();
                     if (i + 1 < nblk) ptx::tmem_ld_32x32b_x32(t_lane, cur[0]);
                 }
@@ -410,53 +459,113 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
 
         // epilogue: O / l
-        bounded_wait(s_full, (uint32_t)(nblk + 1) & 1u, abort_addr, 7);
+        bounded_wait(s_full, (s_base + (uint32_t)nblk + 1u) & 1u, abort_addr, 7);
         ptx::tcgen05_fence_after_sync();
+        if (MULTI) {                                            // the next tile's scores may now be produced
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(step_end);
+        }
         {
+            // O / l goes through shared memory so that the global stores are whole rows: every thread
+            // converts its own row and parks it in the P rows of its warp (32 rows x 64 bytes in each of
+            // the two P buffers, free now that every P.V has retired, and touched by no other warp), then
+            // the warp writes the 32 rows out with 8 (bf16) or 4 (e4m3) lanes per row.
             const float inv = (l_run == 0.f || l_run != l_run) ? 1.f : 1.f / l_run;
-            const int64_t out_off = (int64_t)b * p.out_stride_b + (int64_t)(bh - b * p.H) * p.out_stride_h +
-                                    (int64_t)row * p.out_stride_s;
+            const uint32_t stage = smem_base + L::kPOff + (uint32_t)(quarter * 32) * kAttnBN;   // + kPBytes: second half
 #pragma unroll 1
             for (int h = 0; h < kAttnD / 32; ++h) {
                 uint32_t orow[32];
                 __syncwarp();
                 ptx::tmem_ld_32x32b_x32(t_lane + kAttnOCol + h * 32, orow);
                 ptx::tmem_wait_ld();
-                if (row < p.M) {
-                  for (int dst = 0; dst < p.n_out; ++dst) {
-                    if (p.out_e4m3) {
-                        uint8_t* o = reinterpret_cast<uint8_t*>(p.outs[dst]) + out_off + h * 32;
+                const uint32_t half = stage + (uint32_t)h * L::kPBytes;
+                if (p.out_e4m3) {                                // 32 bytes per row and half: 2 pieces, swizzled by row bit 2
 #pragma unroll
-                        for (int v4 = 0; v4 < 2; ++v4) {
-                            uint32_t w[4];
+                    for (int v4 = 0; v4 < 2; ++v4) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int j = v4 * 16 + q * 4;
-                                w[q] = pack4_e4m3(__uint_as_float(orow[j]) * inv, __uint_as_float(orow[j + 1]) * inv,
-                                                  __uint_as_float(orow[j + 2]) * inv, __uint_as_float(orow[j + 3]) * inv);
-                            }
-                            reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int q = 0; q < 4; ++q) {
+                            const int j = v4 * 16 + q * 4;
+                            w[q] = pack4_e4m3(__uint_as_float(orow[j]) * inv, __uint_as_float(orow[j + 1]) * inv,
+                                              __uint_as_float(orow[j + 2]) * inv, __uint_as_float(orow[j + 3]) * inv);
                         }
-                    } else {
-                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.outs[dst]) + out_off + h * 32;
-#pragma unroll
-                        for (int v4 = 0; v4 < 4; ++v4) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int j = v4 * 8 + q * 2;
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(orow[j]) * inv,
-                                                                          __uint_as_float(orow[j + 1]) * inv);
-                                w[q] = *reinterpret_cast<uint32_t*>(&b2);
-                            }
-                            reinterpret_cast<uint4*>(o)[v4] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
+                        st_shared_v4(half + (uint32_t)lane * 32u + ((((uint32_t)v4) ^ (((uint32_t)lane >> 2) & 1u)) << 4),
+                                     w[0], w[1], w[2], w[3]);
                     }
-                  }
+                } else {                                         // 64 bytes per row and half: 4 pieces, swizzled by row bits 1..2
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int j = v4 * 8 + q * 2;
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(orow[j]) * inv,
+                                                                      __uint_as_float(orow[j + 1]) * inv);
+                            w[q] = *reinterpret_cast<uint32_t*>(&b2);
+                        }
+                        st_shared_v4(half + (uint32_t)lane * 64u + ((((uint32_t)v4) ^ (((uint32_t)lane >> 1) & 3u)) << 4),
+                                     w[0], w[1], w[2], w[3]);
+                    }
                 }
             }
+            const int row_w0 = row - lane;                       // first row of this warp
+            if (p.tma_out) {
+                // one destination: the two staged boxes (32 rows x 32 columns each) go out as TMA stores, which
+                // run while the warp is already at its next tile; rows beyond M are clipped by the map
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && row_w0 < p.M) {
+                    const int head = bh - b * p.H;
+                    const int c1 = p.tma_out == 2 ? row_w0 : head, c2 = p.tma_out == 2 ? head : row_w0;
+                    const int xb = p.out_e4m3 ? 32 : 64;        // bytes per row of one box
+                    ptx::tma_store_4d(&tmap_o, stage, 0, c1, c2, b);
+                    ptx::tma_store_4d(&tmap_o, stage + L::kPBytes, xb, c1, c2, b);
+                    ptx::bulk_commit_group();
+                }
+                continue;
+            }
+            __syncwarp();
+            const int64_t head_off = (int64_t)b * p.out_stride_b + (int64_t)(bh - b * p.H) * p.out_stride_h;
+            if (p.out_e4m3) {
+                const int pc = lane & 3;                          // 16-byte piece of the 64-byte row
+                const uint32_t src = stage + (uint32_t)(pc >> 1) * L::kPBytes;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int rr = (lane >> 2) + 8 * k;
+                    uint4 val;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                 : "r"(src + (uint32_t)rr * 32u + ((((uint32_t)pc & 1u) ^ (((uint32_t)rr >> 2) & 1u)) << 4))
+                                 : "memory");
+                    if (row_w0 + rr < p.M) {
+                        const int64_t off = head_off + (int64_t)(row_w0 + rr) * p.out_stride_s + pc * 16;
+                        for (int dst = 0; dst < p.n_out; ++dst)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.outs[dst]) + off) = val;
+                    }
+                }
+            } else {
+                const int pc = lane & 7;                          // 16-byte piece of the 128-byte row
+                const uint32_t src = stage + (uint32_t)(pc >> 2) * L::kPBytes;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int rr = (lane >> 3) + 4 * k;
+                    uint4 val;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                 : "r"(src + (uint32_t)rr * 64u + ((((uint32_t)pc & 3u) ^ (((uint32_t)rr >> 1) & 3u)) << 4))
+                                 : "memory");
+                    if (row_w0 + rr < p.M) {
+                        const int64_t off = head_off + (int64_t)(row_w0 + rr) * p.out_stride_s + pc * 8;
+                        for (int dst = 0; dst < p.n_out; ++dst)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.outs[dst]) + off) = val;
+                    }
+                }
+            }
+            __syncwarp();                                       // the rows are read out before the next tile's P overwrites them
             if (p.n_out > 1) __threadfence_system();
         }
+        }   // query tiles of this CTA
+        if (p.tma_out && lane == 0) ptx::bulk_wait_group<0>();  // this warp's stores are performed before the CTA may exit
         teardown_barrier();
     }
     // an abandoned wait anywhere in the CTA is reported through the status word
@@ -758,18 +867,57 @@ static int launch_flash_attention(bool v_rows, const void* q, const void* k, con
     p.out_e4m3 = out_dtype == Q8K_DT_E4M3;
     p.out_stride_b = out_stride_b; p.out_stride_h = out_stride_h; p.out_stride_s = out_stride_s;
 
+    // One destination: the epilogue stores through a 4-D map of the output (bytes of a head row; rows and
+    // heads in the order of their strides; batch), 32-row boxes of half a head row, swizzled like the staging.
+    CUtensorMap to = tq;
+    p.tma_out = 0;
+    if (n_out == 1) {
+        const uint64_t esz = p.out_e4m3 ? 1 : 2;
+        const bool rows_first = out_stride_s <= out_stride_h;
+        const uint64_t s_lo = (uint64_t)(rows_first ? out_stride_s : out_stride_h) * esz;
+        const uint64_t s_hi = (uint64_t)(rows_first ? out_stride_h : out_stride_s) * esz;
+        const uint64_t s_b = (uint64_t)out_stride_b * esz;
+        const bool nested = s_lo >= 64 * esz && s_hi % s_lo == 0 && (B == 1 || (s_b >= s_hi && s_b % s_hi == 0));
+        if (nested) {
+            const uint64_t dims[4] = {64 * esz, (uint64_t)(rows_first ? M : H), (uint64_t)(rows_first ? H : M), (uint64_t)B};
+            const uint64_t strides[3] = {s_lo, s_hi, B == 1 ? s_hi * dims[2] : s_b};
+            const uint32_t box[4] = {(uint32_t)(32 * esz), rows_first ? 32u : 1u, rows_first ? 1u : 32u, 1u};
+            if (int rc = make_byte_tensor_map(&to, out, 4, dims, strides, box, (int)(32 * esz), op)) return rc;
+            p.tma_out = rows_first ? 2 : 1;
+        }
+    }
+
     // The warpgroups re-budget registers with setmaxnreg; an increase blocks until the CTA's pool
     // has room, so the pool the kernel was compiled for must cover the three budgets.
     static_assert(2 * kAttnRegsLaunch == kAttnRegsIo + kAttnRegsSoftmax, "register budgets");
-    auto kern = v_rows ? flash_attn_fp8_kernel<true> : flash_attn_fp8_kernel<false>;
+    // Short key sequences (all of K and V fit the ring): a CTA walks over several query tiles of its
+    // (batch, head); as many CTAs per (batch, head) as fill the device once at three CTAs per SM.
+    const int q_tiles = (M + kAttnBM - 1) / kAttnBM;
+    const bool multi = (N + kAttnBN - 1) / kAttnBN <= kAttnKS && q_tiles > 1;
+    int ctas_per_bh = q_tiles;
+    if (multi) {
+        static int num_sms = 0;
+        if (num_sms == 0) {
+            int dev = 0, n = 0;
+            Q8K_CUDA_OK(cudaGetDevice(&dev));
+            Q8K_CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+            num_sms = n;
+        }
+        int g_max = (int)((uint64_t)(3 * num_sms) / BH);
+        g_max = g_max < 1 ? 1 : (g_max > q_tiles ? q_tiles : g_max);
+        const int tiles_per_cta = (q_tiles + g_max - 1) / g_max;
+        ctas_per_bh = (q_tiles + tiles_per_cta - 1) / tiles_per_cta;
+    }
+    auto kern = v_rows ? (multi ? flash_attn_fp8_kernel<true, true> : flash_attn_fp8_kernel<true, false>)
+                       : (multi ? flash_attn_fp8_kernel<false, true> : flash_attn_fp8_kernel<false, false>);
     cudaFuncAttributes fattr;
     Q8K_CUDA_OK(cudaFuncGetAttributes(&fattr, kern));
     Q8K_REQUIRE(fattr.numRegs >= kAttnRegsLaunch, Q8K_ERR_CUDA,
                 "%s: kernel was built with %d registers per thread, %d needed for the warpgroup budgets", op,
                 fattr.numRegs, kAttnRegsLaunch);
     Q8K_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::kDynamic));
-    dim3 grid((unsigned)((M + kAttnBM - 1) / kAttnBM), (unsigned)BH);
-    kern<<<grid, kAttnThreads, AttnSmem::kDynamic, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    dim3 grid((unsigned)ctas_per_bh, (unsigned)BH);
+    kern<<<grid, kAttnThreads, AttnSmem::kDynamic, (cudaStream_t)stream>>>(tq, tk, tv, to, p);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }
