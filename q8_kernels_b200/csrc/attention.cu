@@ -619,12 +619,7 @@ attn_prep_qk_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ o
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(v[j], scale);
     }
-    if (row_ok) {
-        union { uint2 v2; uint8_t bts[8]; } o;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o.bts[j] = float_to_e4m3_c10(v[j]);
-        *reinterpret_cast<uint2*>(out + (((int64_t)b * H + h) * S + s) * 64 + sub * 8) = o.v2;
-    }
+    if (row_ok) *reinterpret_cast<uint2*>(out + (((int64_t)b * H + h) * S + s) * 64 + sub * 8) = pack8_e4m3_c10(v);
 }
 
 // Q / K after their projection, fused: RMS norm over all H*64 channels with an fp32 weight (bf16
@@ -633,90 +628,102 @@ attn_prep_qk_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ o
 // CTA per token row, 8 elements per thread (thread t owns channels 8t..8t+7, head t/8).  The
 // roundings are those of the separate kernels (rms_norm_kernel, rope_kernel, attn_prep_qk_kernel);
 // only the summation order of the mean square differs from rms_norm_kernel.
-// With a second tensor (x2 / norm_w2 / out2 non-null: K next to Q, same shape and row stride) the
-// grid is twice as long and neighbouring CTAs handle Q and K of the same token, so the rotary
-// table row is fetched from DRAM once.
+// PAIR (x2 / norm_w2 / out2: K next to Q, same shape and row stride): the CTA handles the Q row and the
+// K row of its token, so the rotary table row is loaded once for both and the two chains interleave.
+template <bool PAIR>
 __global__ void __launch_bounds__(1024)
 attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x2,
                               int64_t x_row_stride, const float* __restrict__ norm_w,
                               const float* __restrict__ norm_w2, const float* __restrict__ cos_t,
                               const float* __restrict__ sin_t, uint8_t* __restrict__ out,
                               uint8_t* __restrict__ out2, int H, int S, int apply_hadamard, float scale) {
-    __shared__ float red[32];
+    constexpr int NX = PAIR ? 2 : 1;                           // PAIR: the Q row and the K row of one token in one CTA
+    __shared__ float red[NX][32];
     const int t = threadIdx.x;
     const int lane = t & 31;
     const int dim = H * 64;
-    int64_t row = blockIdx.x;                                  // b * S + s
-    if (x2 != nullptr) {
-        if (blockIdx.x & 1) { x = x2; norm_w = norm_w2; out = out2; }
-        row = blockIdx.x >> 1;
-    }
+    const int64_t row = blockIdx.x;                            // b * S + s
     const int s_idx = (int)(row % S);
     const int64_t b = row / S;
-    float v[8];
-    load_vec<__nv_bfloat16, 8>(x + row * x_row_stride + t * 8, v);
-    // the weight and rotary rows do not depend on the reduction: fetch them under its latency
-    float wv[8], c[8], sn[8];
-    load_vec<float, 8>(norm_w + t * 8, wv);
+    float v[NX][8];
+    load_vec<__nv_bfloat16, 8>(x + row * x_row_stride + t * 8, v[0]);
+    if (PAIR) load_vec<__nv_bfloat16, 8>(x2 + row * x_row_stride + t * 8, v[NX - 1]);
+    // the weights and rotary rows do not depend on the reduction: fetch them under its latency; the
+    // rotary row is the same for Q and K
+    float wv[NX][8], c[8], sn[8];
+    load_vec<float, 8>(norm_w + t * 8, wv[0]);
+    if (PAIR) load_vec<float, 8>(norm_w2 + t * 8, wv[NX - 1]);
     if (cos_t != nullptr) {
         load_vec<float, 8>(cos_t + (int64_t)s_idx * dim + t * 8, c);
         load_vec<float, 8>(sin_t + (int64_t)s_idx * dim + t * 8, sn);
     }
 
-    float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
-    ss = warp_sum(ss);
-    if (lane == 0) red[t >> 5] = ss;
+    for (int w = 0; w < NX; ++w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(v[w][j], v[w][j], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) red[w][t >> 5] = ss;
+    }
     __syncthreads();
-    float tot = red[0];
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
-    const float r = rsqrtf(tot * (1.0f / (float)dim));
 
+    const int h = t >> 3, sub = t & 7;
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-        v[j] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v[j], r), wv[j])));
-
-    if (cos_t != nullptr) {
-        float o[8];
+    for (int w = 0; w < NX; ++w) {
+        float tot = red[w][0];
+        for (int i = 1; i < (int)(blockDim.x >> 5); ++i) tot += red[w][i];
+        const float r = rsqrtf(tot * (1.0f / (float)dim));
+        float (&u)[8] = v[w];
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
-            o[j]     = __fadd_rn(__fmul_rn(-v[j + 1], sn[j]), __fmul_rn(v[j], c[j]));
-            o[j + 1] = __fadd_rn(__fmul_rn(v[j], sn[j + 1]), __fmul_rn(v[j + 1], c[j + 1]));
+            u[j] = __fmul_rn(__fmul_rn(u[j], r), wv[w][j]);
+            u[j + 1] = __fmul_rn(__fmul_rn(u[j + 1], r), wv[w][j + 1]);
+            round_through_bf16x2(u[j], u[j + 1]);
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(o[j]));
-    }
 
-    if (apply_hadamard) {
+        if (cos_t != nullptr) {
+            float o[8];
 #pragma unroll
-        for (int st = 1; st < 8; st <<= 1) {
+            for (int j = 0; j < 8; j += 2) {
+                o[j]     = __fadd_rn(__fmul_rn(-u[j + 1], sn[j]), __fmul_rn(u[j], c[j]));
+                o[j + 1] = __fadd_rn(__fmul_rn(u[j], sn[j + 1]), __fmul_rn(u[j + 1], c[j + 1]));
+            }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int lo = j & (st - 1);
-                const int i = ((j - lo) << 1) + lo;
-                const float a = v[i], bb = v[i + st];
-                v[i] = __fadd_rn(a, bb);
-                v[i + st] = __fsub_rn(a, bb);
+            for (int j = 0; j < 8; j += 2) {
+                u[j] = o[j];
+                u[j + 1] = o[j + 1];
+                round_through_bf16x2(u[j], u[j + 1]);
             }
         }
+
+        if (apply_hadamard) {
 #pragma unroll
-        for (int mk = 1; mk < 8; mk <<= 1) {
-            const float sign = (lane & mk) ? -1.f : 1.f;
+            for (int st = 1; st < 8; st <<= 1) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float other = __shfl_xor_sync(0xffffffffu, v[j], mk);
-                v[j] = __fmaf_rn(sign, v[j], other);           // other - v for the upper lane, v + other for the lower: exact
+                for (int j = 0; j < 4; ++j) {
+                    const int lo = j & (st - 1);
+                    const int i = ((j - lo) << 1) + lo;
+                    const float a = u[i], bb = u[i + st];
+                    u[i] = __fadd_rn(a, bb);
+                    u[i + st] = __fsub_rn(a, bb);
+                }
             }
-        }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(v[j], scale);
+            for (int mk = 1; mk < 8; mk <<= 1) {
+                const float sign = (lane & mk) ? -1.f : 1.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float other = __shfl_xor_sync(0xffffffffu, u[j], mk);
+                    u[j] = __fmaf_rn(sign, u[j], other);       // other - u for the upper lane, u + other for the lower: exact
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) u[j] = __fmul_rn(u[j], scale);
+        }
+        uint8_t* dst = w == 0 ? out : out2;
+        *reinterpret_cast<uint2*>(dst + ((b * H + h) * S + s_idx) * 64 + sub * 8) = pack8_e4m3_c10(u);
     }
-    union { uint2 v2; uint8_t bts[8]; } o8;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o8.bts[j] = float_to_e4m3_c10(v[j]);
-    const int h = t >> 3, sub = t & 7;
-    *reinterpret_cast<uint2*>(out + ((b * H + h) * S + s_idx) * 64 + sub * 8) = o8.v2;
 }
 
 // V: [B,S,H,64] bf16 view -> vt [B,H,64,S_pad] e4m3, zero padded along S.
@@ -987,7 +994,7 @@ extern "C" int q8k_qk_norm_rope_prep(const void* x, int64_t x_row_stride, const 
     Q8K_REQUIRE(aligned16(x) && aligned16(norm_w) && aligned16(cos_t) && aligned16(sin_t) && aligned16(out8),
                 Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
     Q8K_REQUIRE((int64_t)B * S <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
-    attn_qk_norm_rope_prep_kernel<<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
+    attn_qk_norm_rope_prep_kernel<false><<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)x, nullptr, x_row_stride, norm_w, nullptr, cos_t, sin_t, (uint8_t*)out8, nullptr, H, S,
         apply_hadamard, qk_scale);
     Q8K_CUDA_OK(cudaGetLastError());
@@ -1009,7 +1016,7 @@ extern "C" int q8k_qk_norm_rope_prep_pair(const void* xq, const void* xk, int64_
                     aligned16(sin_t) && aligned16(outq8) && aligned16(outk8),
                 Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
     Q8K_REQUIRE((int64_t)B * S * 2 <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
-    attn_qk_norm_rope_prep_kernel<<<(unsigned)((int64_t)B * S * 2), H * 8, 0, (cudaStream_t)stream>>>(
+    attn_qk_norm_rope_prep_kernel<true><<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)xq, (const __nv_bfloat16*)xk, x_row_stride, norm_wq, norm_wk, cos_t, sin_t, (uint8_t*)outq8,
         (uint8_t*)outk8, H, S, apply_hadamard, qk_scale);
     Q8K_CUDA_OK(cudaGetLastError());

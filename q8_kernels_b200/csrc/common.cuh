@@ -80,6 +80,33 @@ __device__ __forceinline__ uint8_t float_to_e4m3_c10(float x) {
     return r;
 }
 
+// Eight values at once, same bytes as float_to_e4m3_c10 on each: four packed saturating conversions, and
+// only if some |x| exceeds 464 or a NaN went in (the conversion returns 0x7F for it, whatever its sign)
+// the element-wise form.
+__device__ __forceinline__ uint2 pack8_e4m3_c10(const float (&x)[8]) {
+    uint2 w;
+    w.x = (uint32_t)float2_to_e4m3x2_sat(x[0], x[1]) | ((uint32_t)float2_to_e4m3x2_sat(x[2], x[3]) << 16);
+    w.y = (uint32_t)float2_to_e4m3x2_sat(x[4], x[5]) | ((uint32_t)float2_to_e4m3x2_sat(x[6], x[7]) << 16);
+    const float m = fmaxf(fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))),
+                          fmaxf(fmaxf(fabsf(x[4]), fabsf(x[5])), fmaxf(fabsf(x[6]), fabsf(x[7]))));
+    const uint32_t nan_bytes = (((w.x & 0x7f7f7f7fu) + 0x01010101u) | ((w.y & 0x7f7f7f7fu) + 0x01010101u)) & 0x80808080u;
+    if (m > 464.0f || nan_bytes != 0u) {
+        union { uint2 v; uint8_t b[8]; } o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.b[j] = float_to_e4m3_c10(x[j]);
+        w = o.v;
+    }
+    return w;
+}
+
+// Both values rounded to bf16 (nearest even) and widened again: one packed conversion and two bit moves.
+__device__ __forceinline__ void round_through_bf16x2(float& a, float& b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+    a = __uint_as_float(w << 16);
+    b = __uint_as_float(w & 0xffff0000u);
+}
+
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
