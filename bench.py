@@ -211,11 +211,30 @@ def time_region(fn, steps: int, warmup: int, barrier=None):
     return start.elapsed_time(end), launches
 
 
-def timed(fn, iters, warm=3):
+def timed(fn, iters, warm=3, graph=True):
+    """Average device time of one call.  The `iters` calls are captured into one CUDA graph and the replay is
+    timed, so that a kernel of a few tens of microseconds is not measured at the rate at which Python can
+    launch it (callables that rotate over buffers keep doing so: each captured call has its own operands)."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                keep = [fn() for _ in range(iters)]            # outputs live in the graph's pool
+            g.replay()
+            torch.cuda.synchronize()
+            s.record()
+            g.replay()
+            e.record()
+            torch.cuda.synchronize()
+            ms = s.elapsed_time(e) / iters
+            del keep, g
+            return ms
+        except RuntimeError:
+            torch.cuda.synchronize()
     s.record()
     for _ in range(iters):
         fn()
@@ -322,10 +341,11 @@ def detail_gemm_tables(q8, dev, acts, wts, kind):
     return per
 
 
-def detail_scaled_mm(dev, acts, wts):
+def detail_scaled_mm(dev, acts, wts, steps):
     """The same FP8 sweep through cuBLASLt (``torch._scaled_mm`` with per-row / per-column scales,
     bf16 output; bias + GELU cases run without the GELU, which it cannot fuse): a same-run, same-box
-    library number to set the hand-written kernel against."""
+    library number to set the hand-written kernel against.  It runs as many steps as the headline loop,
+    so that both numbers are taken in the same power state (a long loop sits at the power cap)."""
     try:
         def step():
             for (m, k, n, fused) in sweep_cases():
@@ -333,8 +353,8 @@ def detail_scaled_mm(dev, acts, wts):
                 wq, ws, bias = wts[(n, k)]
                 torch._scaled_mm(xq, wq.t(), scale_a=xs.view(m, 1), scale_b=ws.view(1, n),
                                  bias=bias.to(torch.bfloat16) if fused else None, out_dtype=torch.bfloat16)
-        ms = timed(step, 5, warm=2)
-        return {"tflops": round(sweep_flops() / ms / 1e9, 1), "ms_per_step": round(ms, 4),
+        ms = timed(step, steps, warm=3, graph=False)
+        return {"tflops": round(sweep_flops() / ms / 1e9, 1), "ms_per_step": round(ms, 4), "steps": steps,
                 "what": "torch._scaled_mm, e4m3 x e4m3, row-wise scales, bf16 out, same 16 launches (no GELU)"}
     except Exception as exc:                                   # noqa: BLE001  (library path: report, do not fail the bench)
         return {"tflops": None, "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
@@ -799,7 +819,7 @@ def main():
     if not args.no_detail:
         detail = {}
         if rank == 0:
-            sm_ref = detail_scaled_mm(dev, acts, wts)
+            sm_ref = detail_scaled_mm(dev, acts, wts, args.steps)
             detail["fp8_sweep_cublaslt_scaled_mm"] = sm_ref
             if sm_ref.get("tflops"):
                 line["roofline"]["frac_vs_scaled_mm"] = round(flops / ms_step / 1e9 / sm_ref["tflops"], 4)

@@ -241,6 +241,15 @@ Q8K_API int q8k_qk_norm_rope_prep(const void* x, int64_t x_row_stride, const flo
 Q8K_API int q8k_qk_norm_rope_prep_pair(const void* xq, const void* xk, int64_t x_row_stride, const float* norm_wq,
                                const float* norm_wk, const float* cos_t, const float* sin_t, void* outq8,
                                void* outk8, int B, int S, int H, int apply_hadamard, float qk_scale, void* stream);
+/* q8k_qk_norm_rope_prep_pair plus the V of the same self-attention (a third slice of the fused projection
+ * output, same row stride): V is only cast to e4m3 (the .to(float8_e4m3fn) of
+ * q8_kernels/functional/flash_attention.py:48) and written as rows [B,H,S,64], the layout
+ * q8k_flash_attention_v_rows reads.  One launch for everything between the QKV projection and the
+ * attention kernel.  xq, norm_wq and outq8 may all be NULL: K and V only (cross-attention, where Q is
+ * projected from another tensor).                                                                */
+Q8K_API int q8k_qkv_prep(const void* xq, const void* xk, const void* xv, int64_t x_row_stride, const float* norm_wq,
+                 const float* norm_wk, const float* cos_t, const float* sin_t, void* outq8, void* outk8,
+                 void* outv8, int B, int S, int H, int apply_hadamard, float qk_scale, void* stream);
 Q8K_API int q8k_attention_prep_v(const void* v, void* vt8, int B, int H, int S_kv, int64_t v_stride_b,
                          int64_t v_stride_s, int64_t v_stride_h, void* stream);
 

@@ -69,6 +69,8 @@ SIGNATURES = {
                                        _c_f32, _c_ptr]),
     "q8k_qk_norm_rope_prep_pair": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
                                             _c_int, _c_int, _c_int, _c_f32, _c_ptr]),
+    "q8k_qkv_prep": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
+                              _c_int, _c_int, _c_int, _c_f32, _c_ptr]),
     "q8k_attention_prep_v": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_ptr]),
     "q8k_linear_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "q8k_linear": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,

@@ -628,31 +628,39 @@ attn_prep_qk_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ o
 // CTA per token row, 8 elements per thread (thread t owns channels 8t..8t+7, head t/8).  The
 // roundings are those of the separate kernels (rms_norm_kernel, rope_kernel, attn_prep_qk_kernel);
 // only the summation order of the mean square differs from rms_norm_kernel.
-// PAIR (x2 / norm_w2 / out2: K next to Q, same shape and row stride): the CTA handles the Q row and the
-// K row of its token, so the rotary table row is loaded once for both and the two chains interleave.
-template <bool PAIR>
+// MODE 0: one row per CTA.  MODE 1 (x2 / norm_w2 / out2: K next to Q, same shape and row stride): the CTA
+// handles the Q row and the K row of its token, so the rotary table row is loaded once for both and the
+// two chains interleave.  MODE 0 and 1 with x3 / out3 also cast the token's V row to e4m3 (no norm, no
+// rotation), written head-major like the others.  MODE 2 (no rotary tables, an even number of rows): the CTA handles
+// two consecutive rows of x for the same interleaving.
+template <int MODE>
 __global__ void __launch_bounds__(1024)
 attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x2,
-                              int64_t x_row_stride, const float* __restrict__ norm_w,
-                              const float* __restrict__ norm_w2, const float* __restrict__ cos_t,
-                              const float* __restrict__ sin_t, uint8_t* __restrict__ out,
-                              uint8_t* __restrict__ out2, int H, int S, int apply_hadamard, float scale) {
-    constexpr int NX = PAIR ? 2 : 1;                           // PAIR: the Q row and the K row of one token in one CTA
+                              const __nv_bfloat16* __restrict__ x3, int64_t x_row_stride,
+                              const float* __restrict__ norm_w, const float* __restrict__ norm_w2,
+                              const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                              uint8_t* __restrict__ out, uint8_t* __restrict__ out2, uint8_t* __restrict__ out3,
+                              int H, int S, int apply_hadamard, float scale) {
+    constexpr bool PAIR = MODE == 1;
+    constexpr int NX = MODE == 0 ? 1 : 2;
     __shared__ float red[NX][32];
     const int t = threadIdx.x;
     const int lane = t & 31;
     const int dim = H * 64;
-    const int64_t row = blockIdx.x;                            // b * S + s
+    const int64_t row = MODE == 2 ? (int64_t)blockIdx.x * 2 : (int64_t)blockIdx.x;   // b * S + s
     const int s_idx = (int)(row % S);
     const int64_t b = row / S;
+    if (MODE == 2) { x2 = x + x_row_stride; norm_w2 = norm_w; }
     float v[NX][8];
     load_vec<__nv_bfloat16, 8>(x + row * x_row_stride + t * 8, v[0]);
-    if (PAIR) load_vec<__nv_bfloat16, 8>(x2 + row * x_row_stride + t * 8, v[NX - 1]);
+    if (NX == 2) load_vec<__nv_bfloat16, 8>(x2 + row * x_row_stride + t * 8, v[NX - 1]);
+    float v3[8];
+    if (MODE != 2 && x3 != nullptr) load_vec<__nv_bfloat16, 8>(x3 + row * x_row_stride + t * 8, v3);
     // the weights and rotary rows do not depend on the reduction: fetch them under its latency; the
     // rotary row is the same for Q and K
     float wv[NX][8], c[8], sn[8];
     load_vec<float, 8>(norm_w + t * 8, wv[0]);
-    if (PAIR) load_vec<float, 8>(norm_w2 + t * 8, wv[NX - 1]);
+    if (NX == 2) load_vec<float, 8>(norm_w2 + t * 8, wv[NX - 1]);
     if (cos_t != nullptr) {
         load_vec<float, 8>(cos_t + (int64_t)s_idx * dim + t * 8, c);
         load_vec<float, 8>(sin_t + (int64_t)s_idx * dim + t * 8, sn);
@@ -669,6 +677,8 @@ attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bf
     __syncthreads();
 
     const int h = t >> 3, sub = t & 7;
+    if (MODE != 2 && x3 != nullptr)
+        *reinterpret_cast<uint2*>(out3 + ((b * H + h) * S + s_idx) * 64 + sub * 8) = pack8_e4m3_c10(v3);
 #pragma unroll
     for (int w = 0; w < NX; ++w) {
         float tot = red[w][0];
@@ -721,8 +731,13 @@ attn_qk_norm_rope_prep_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bf
 #pragma unroll
             for (int j = 0; j < 8; ++j) u[j] = __fmul_rn(u[j], scale);
         }
-        uint8_t* dst = w == 0 ? out : out2;
-        *reinterpret_cast<uint2*>(dst + ((b * H + h) * S + s_idx) * 64 + sub * 8) = pack8_e4m3_c10(u);
+        if (MODE == 2) {                                        // second row: the next token (possibly of the next batch entry)
+            const int64_t rw = row + w;
+            *reinterpret_cast<uint2*>(out + (((rw / S) * H + h) * S + (rw % S)) * 64 + sub * 8) = pack8_e4m3_c10(u);
+        } else {
+            uint8_t* dst = w == 0 ? out : out2;
+            *reinterpret_cast<uint2*>(dst + ((b * H + h) * S + s_idx) * 64 + sub * 8) = pack8_e4m3_c10(u);
+        }
     }
 }
 
@@ -994,9 +1009,43 @@ extern "C" int q8k_qk_norm_rope_prep(const void* x, int64_t x_row_stride, const 
     Q8K_REQUIRE(aligned16(x) && aligned16(norm_w) && aligned16(cos_t) && aligned16(sin_t) && aligned16(out8),
                 Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
     Q8K_REQUIRE((int64_t)B * S <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
-    attn_qk_norm_rope_prep_kernel<false><<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)x, nullptr, x_row_stride, norm_w, nullptr, cos_t, sin_t, (uint8_t*)out8, nullptr, H, S,
-        apply_hadamard, qk_scale);
+    if (cos_t == nullptr && ((int64_t)B * S) % 2 == 0)
+        attn_qk_norm_rope_prep_kernel<2><<<(unsigned)((int64_t)B * S / 2), H * 8, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)x, nullptr, nullptr, x_row_stride, norm_w, nullptr, nullptr, nullptr, (uint8_t*)out8,
+            nullptr, nullptr, H, S, apply_hadamard, qk_scale);
+    else
+        attn_qk_norm_rope_prep_kernel<0><<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)x, nullptr, nullptr, x_row_stride, norm_w, nullptr, cos_t, sin_t, (uint8_t*)out8,
+            nullptr, nullptr, H, S, apply_hadamard, qk_scale);
+    Q8K_CUDA_OK(cudaGetLastError());
+    return Q8K_OK;
+}
+
+static int launch_qkv_prep(const char* op, const void* xq, const void* xk, const void* xv, int64_t x_row_stride,
+                           const float* norm_wq, const float* norm_wk, const float* cos_t, const float* sin_t,
+                           void* outq8, void* outk8, void* outv8, int B, int S, int H, int apply_hadamard,
+                           float qk_scale, void* stream) {
+    Q8K_REQUIRE(xk && norm_wk && outk8, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
+    Q8K_REQUIRE((xq == nullptr) == (outq8 == nullptr) && (xq == nullptr) == (norm_wq == nullptr), Q8K_ERR_INVALID_ARG,
+                "%s: give q, its norm weight and its output, or none of them", op);
+    Q8K_REQUIRE((xv == nullptr) == (outv8 == nullptr), Q8K_ERR_INVALID_ARG, "%s: give both v and its output or neither", op);
+    Q8K_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), Q8K_ERR_INVALID_ARG, "%s: give both rotary tables or neither", op);
+    Q8K_REQUIRE(B > 0 && S > 0 && H > 0 && H <= 128, Q8K_ERR_INVALID_ARG, "%s: bad shape B=%d S=%d H=%d (H <= 128)", op, B, S, H);
+    Q8K_REQUIRE(H % 4 == 0, Q8K_ERR_UNSUPPORTED, "%s: H must be a multiple of 4", op);
+    Q8K_REQUIRE(x_row_stride >= (int64_t)H * 64 && x_row_stride % 8 == 0, Q8K_ERR_INVALID_ARG,
+                "%s: row stride must be >= H*64 and a multiple of 8 elements", op);
+    Q8K_REQUIRE(aligned16(xq) && aligned16(xk) && aligned16(xv) && aligned16(norm_wq) && aligned16(norm_wk) &&
+                    aligned16(cos_t) && aligned16(sin_t) && aligned16(outq8) && aligned16(outk8) && aligned16(outv8),
+                Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
+    Q8K_REQUIRE((int64_t)B * S <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
+    if (xq != nullptr)
+        attn_qk_norm_rope_prep_kernel<1><<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)xq, (const __nv_bfloat16*)xk, (const __nv_bfloat16*)xv, x_row_stride, norm_wq, norm_wk, cos_t,
+            sin_t, (uint8_t*)outq8, (uint8_t*)outk8, (uint8_t*)outv8, H, S, apply_hadamard, qk_scale);
+    else                                                       // K and V only (cross-attention: Q comes from another tensor)
+        attn_qk_norm_rope_prep_kernel<0><<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)xk, nullptr, (const __nv_bfloat16*)xv, x_row_stride, norm_wk, nullptr, cos_t, sin_t,
+            (uint8_t*)outk8, nullptr, (uint8_t*)outv8, H, S, apply_hadamard, qk_scale);
     Q8K_CUDA_OK(cudaGetLastError());
     return Q8K_OK;
 }
@@ -1005,22 +1054,17 @@ extern "C" int q8k_qk_norm_rope_prep_pair(const void* xq, const void* xk, int64_
                                           const float* norm_wk, const float* cos_t, const float* sin_t, void* outq8,
                                           void* outk8, int B, int S, int H, int apply_hadamard, float qk_scale,
                                           void* stream) {
-    const char* op = "qk_norm_rope_prep_pair";
-    Q8K_REQUIRE(xq && xk && norm_wq && norm_wk && outq8 && outk8, Q8K_ERR_INVALID_ARG, "%s: null pointer", op);
-    Q8K_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), Q8K_ERR_INVALID_ARG, "%s: give both rotary tables or neither", op);
-    Q8K_REQUIRE(B > 0 && S > 0 && H > 0 && H <= 128, Q8K_ERR_INVALID_ARG, "%s: bad shape B=%d S=%d H=%d (H <= 128)", op, B, S, H);
-    Q8K_REQUIRE(H % 4 == 0, Q8K_ERR_UNSUPPORTED, "%s: H must be a multiple of 4", op);
-    Q8K_REQUIRE(x_row_stride >= (int64_t)H * 64 && x_row_stride % 8 == 0, Q8K_ERR_INVALID_ARG,
-                "%s: row stride must be >= H*64 and a multiple of 8 elements", op);
-    Q8K_REQUIRE(aligned16(xq) && aligned16(xk) && aligned16(norm_wq) && aligned16(norm_wk) && aligned16(cos_t) &&
-                    aligned16(sin_t) && aligned16(outq8) && aligned16(outk8),
-                Q8K_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", op);
-    Q8K_REQUIRE((int64_t)B * S * 2 <= 0x7fffffffLL, Q8K_ERR_TOO_LARGE, "%s: too many rows", op);
-    attn_qk_norm_rope_prep_kernel<true><<<(unsigned)((int64_t)B * S), H * 8, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)xq, (const __nv_bfloat16*)xk, x_row_stride, norm_wq, norm_wk, cos_t, sin_t, (uint8_t*)outq8,
-        (uint8_t*)outk8, H, S, apply_hadamard, qk_scale);
-    Q8K_CUDA_OK(cudaGetLastError());
-    return Q8K_OK;
+    Q8K_REQUIRE(xq != nullptr, Q8K_ERR_INVALID_ARG, "qk_norm_rope_prep_pair: null pointer");
+    return launch_qkv_prep("qk_norm_rope_prep_pair", xq, xk, nullptr, x_row_stride, norm_wq, norm_wk, cos_t, sin_t, outq8,
+                           outk8, nullptr, B, S, H, apply_hadamard, qk_scale, stream);
+}
+
+extern "C" int q8k_qkv_prep(const void* xq, const void* xk, const void* xv, int64_t x_row_stride, const float* norm_wq,
+                            const float* norm_wk, const float* cos_t, const float* sin_t, void* outq8, void* outk8,
+                            void* outv8, int B, int S, int H, int apply_hadamard, float qk_scale, void* stream) {
+    Q8K_REQUIRE(xv != nullptr && outv8 != nullptr, Q8K_ERR_INVALID_ARG, "qkv_prep: null pointer");
+    return launch_qkv_prep("qkv_prep", xq, xk, xv, x_row_stride, norm_wq, norm_wk, cos_t, sin_t, outq8, outk8, outv8, B, S,
+                           H, apply_hadamard, qk_scale, stream);
 }
 
 extern "C" int q8k_attention_prep_v(const void* v, void* vt8, int B, int H, int S_kv, int64_t v_stride_b,

@@ -120,19 +120,16 @@ class Attention(nn.Module):
             if encoder_hidden_states is None:
                 w, b, sc = self._stacked("qkv", (self.to_q, self.to_k, self.to_v))
                 qkv = self._mm(hq, w, b, hs, sc)
-                q8_, k8_ = native.qk_norm_rope_prep_pair(qkv[..., :C], qkv[..., C:2 * C], self.q_norm.weight,
-                                                         self.k_norm.weight, freqs_cis if rope_here else None, heads,
-                                                         True, scale)
-                value = qkv[..., 2 * C:]
+                # V as rows [B,H,S,64]: the tensor core reads it MN-major, so the reference's transpose is never made
+                q8_, k8_, vt8 = native.qk_norm_rope_prep_pair(qkv[..., :C], qkv[..., C:2 * C], self.q_norm.weight,
+                                                              self.k_norm.weight, freqs_cis if rope_here else None,
+                                                              heads, True, scale, xv=qkv[..., 2 * C:])
             else:
                 query = self.to_q(hq, hs, out_dtype=mm_out_dtype)
                 w, b, sc = self._stacked("kv", (self.to_k, self.to_v))
                 kv = self._mm(kq, w, b, ks, sc)
                 q8_ = native.qk_norm_rope_prep(query, self.q_norm.weight, None, heads, True, scale)
-                k8_ = native.qk_norm_rope_prep(kv[..., :C], self.k_norm.weight, None, heads, True, scale)
-                value = kv[..., C:]
-            # V as rows [B,H,S,64]: the tensor core reads it MN-major, so the reference's transpose is never made
-            vt8 = native.attention_cast_rows(value.unflatten(-1, (heads, self.head_dim)).transpose(1, 2))
+                k8_, vt8 = native.kv_prep(kv[..., :C], kv[..., C:], self.k_norm.weight, heads, True, scale)
             if head_shard is not None:
                 # projections, q/k norm (it spans all heads) and RoPE ran replicated; the attention core
                 # takes this rank's heads and the channel slices are gathered before the output projection

@@ -521,22 +521,52 @@ def qk_norm_rope_prep(x: torch.Tensor, norm_w: torch.Tensor, freqs_cis, num_head
     return out
 
 
+def kv_prep(xk: torch.Tensor, xv: torch.Tensor, norm_wk: torch.Tensor, num_heads: int, apply_hadamard: bool,
+            qk_scale: float):
+    """K and V of a cross-attention (two column slices of one fused projection output, same strides) in one
+    launch: K as qk_norm_rope_prep without rotation, V cast to e4m3 rows; returns (k8, v8), each [B,H,S,64]."""
+    dev = require_cuda(xk, xv, norm_wk)
+    C = num_heads * 64
+    for x in (xk, xv):
+        if x.dtype != torch.bfloat16 or x.dim() != 3 or x.shape[2] != C or x.stride(2) != 1:
+            raise Q8KernelError("kv_prep: inputs must be bfloat16 [B,S,H*64] with contiguous channels")
+    if xk.shape != xv.shape:
+        raise Q8KernelError("kv_prep: k and v must have the same shape")
+    B, S, _ = xk.shape
+    ok = all(x.stride(0) == S * x.stride(1) and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0 for x in (xk, xv))
+    if not ok or xk.stride() != xv.stride():
+        xk, xv = xk.contiguous(), xv.contiguous()
+    if norm_wk.dtype != torch.float32 or norm_wk.numel() != C:
+        raise Q8KernelError("kv_prep: the norm weight must be float32 [H*64]")
+    outk = torch.empty((B, num_heads, S, 64), dtype=E4M3, device=dev)
+    outv = torch.empty((B, num_heads, S, 64), dtype=E4M3, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.q8k_qkv_prep(None, ptr(xk), ptr(xv), xk.stride(1), None, ptr(norm_wk.contiguous()), None, None, None,
+                               ptr(outk), ptr(outv), B, S, num_heads, int(bool(apply_hadamard)), float(qk_scale),
+                               stream_ptr(dev)), "qkv_prep")
+    return outk, outv
+
+
 def qk_norm_rope_prep_pair(xq: torch.Tensor, xk: torch.Tensor, norm_wq: torch.Tensor, norm_wk: torch.Tensor, freqs_cis,
-                           num_heads: int, apply_hadamard: bool, qk_scale: float):
+                           num_heads: int, apply_hadamard: bool, qk_scale: float, xv: Optional[torch.Tensor] = None):
     """qk_norm_rope_prep for the Q and K of one self-attention in a single launch (same shape and
     strides, e.g. column slices of a fused projection output); returns (q8, k8), each e4m3 [B,H,S,64],
-    byte-identical to two separate calls."""
-    dev = require_cuda(xq, xk, norm_wq, norm_wk)
+    byte-identical to two separate calls.  With ``xv`` (a third slice of the same kind) the launch also
+    casts V to e4m3 rows [B,H,S,64] (what attention_cast_rows gives) and (q8, k8, v8) is returned."""
+    dev = require_cuda(xq, xk, norm_wq, norm_wk, xv)
     C = num_heads * 64
-    for x in (xq, xk):
+    xs = (xq, xk) if xv is None else (xq, xk, xv)
+    for x in xs:
         if x.dtype != torch.bfloat16 or x.dim() != 3 or x.shape[2] != C or x.stride(2) != 1:
             raise Q8KernelError("qk_norm_rope_prep_pair: inputs must be bfloat16 [B,S,H*64] with contiguous channels")
-    if xq.shape != xk.shape:
-        raise Q8KernelError("qk_norm_rope_prep_pair: q and k must have the same shape")
+    if any(x.shape != xq.shape for x in xs):
+        raise Q8KernelError("qk_norm_rope_prep_pair: q, k (and v) must have the same shape")
     B, S, _ = xq.shape
-    ok = all(x.stride(0) == S * x.stride(1) and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0 for x in (xq, xk))
-    if not ok or xq.stride() != xk.stride():
-        xq, xk = xq.contiguous(), xk.contiguous()
+    ok = all(x.stride(0) == S * x.stride(1) and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0 for x in xs)
+    if not ok or any(x.stride() != xq.stride() for x in xs):
+        xs = tuple(x.contiguous() for x in xs)
+        xq, xk = xs[0], xs[1]
+        xv = xs[2] if xv is not None else None
     cos = sin = None
     if freqs_cis is not None:
         cos, sin = freqs_cis
@@ -549,11 +579,17 @@ def qk_norm_rope_prep_pair(xq: torch.Tensor, xk: torch.Tensor, norm_wq: torch.Te
     outq = torch.empty((B, num_heads, S, 64), dtype=E4M3, device=dev)
     outk = torch.empty((B, num_heads, S, 64), dtype=E4M3, device=dev)
     with torch.cuda.device(dev):
-        check(lib.q8k_qk_norm_rope_prep_pair(ptr(xq), ptr(xk), xq.stride(1), ptr(norm_wq.contiguous()),
-                                             ptr(norm_wk.contiguous()), ptr(cos), ptr(sin), ptr(outq), ptr(outk), B, S,
-                                             num_heads, int(bool(apply_hadamard)), float(qk_scale), stream_ptr(dev)),
-              "qk_norm_rope_prep_pair")
-    return outq, outk
+        if xv is None:
+            check(lib.q8k_qk_norm_rope_prep_pair(ptr(xq), ptr(xk), xq.stride(1), ptr(norm_wq.contiguous()),
+                                                 ptr(norm_wk.contiguous()), ptr(cos), ptr(sin), ptr(outq), ptr(outk), B, S,
+                                                 num_heads, int(bool(apply_hadamard)), float(qk_scale), stream_ptr(dev)),
+                  "qk_norm_rope_prep_pair")
+            return outq, outk
+        outv = torch.empty((B, num_heads, S, 64), dtype=E4M3, device=dev)
+        check(lib.q8k_qkv_prep(ptr(xq), ptr(xk), ptr(xv), xq.stride(1), ptr(norm_wq.contiguous()),
+                               ptr(norm_wk.contiguous()), ptr(cos), ptr(sin), ptr(outq), ptr(outk), ptr(outv), B, S,
+                               num_heads, int(bool(apply_hadamard)), float(qk_scale), stream_ptr(dev)), "qkv_prep")
+    return outq, outk, outv
 
 
 def attention_prep_v(v: torch.Tensor) -> torch.Tensor:

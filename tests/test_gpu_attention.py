@@ -190,6 +190,52 @@ def test_paired_qk_prep_is_two_single_calls(nat, cuda_device):
     assert torch.equal(Hp.bits(k8), Hp.bits(nat.qk_norm_rope_prep(qkv[..., C:2 * C], wk, fc, H, True, scale)))
 
 
+def test_qkv_prep_adds_the_plain_cast_of_v(nat, cuda_device):
+    """The three slices of a fused QKV projection in one launch: Q and K as in the paired call, V the
+    unscaled e4m3 cast as rows [B,H,S,64]."""
+    B, S, H = 2, 70, 32
+    C = H * 64
+    qkv = Hp.activations(B * S, 3 * C, seed=23).view(B, S, 3 * C).to(cuda_device)
+    wq = (1.0 + 0.1 * torch.randn(C, generator=Hp.gen(1))).to(cuda_device)
+    wk = (1.0 + 0.1 * torch.randn(C, generator=Hp.gen(2))).to(cuda_device)
+    ang = torch.rand(1, S, C, generator=Hp.gen(3)) * 6.28
+    fc = (ang.cos().to(cuda_device), ang.sin().to(cuda_device))
+    scale = 0.125 * math.sqrt(0.125)
+    q8, k8, v8 = nat.qk_norm_rope_prep_pair(qkv[..., :C], qkv[..., C:2 * C], wq, wk, fc, H, True, scale, xv=qkv[..., 2 * C:])
+    q8b, k8b = nat.qk_norm_rope_prep_pair(qkv[..., :C], qkv[..., C:2 * C], wq, wk, fc, H, True, scale)
+    assert torch.equal(Hp.bits(q8), Hp.bits(q8b)) and torch.equal(Hp.bits(k8), Hp.bits(k8b))
+    want_v = qkv[..., 2 * C:].view(B, S, H, 64).transpose(1, 2).to(E4M3)          # torch's cast is the c10 one
+    assert v8.shape == (B, H, S, 64) and torch.equal(Hp.bits(v8), Hp.bits(want_v.contiguous()))
+
+
+def test_kv_prep_is_k_prep_plus_the_cast_of_v(nat, cuda_device):
+    B, S, H = 2, 37, 32
+    C = H * 64
+    kv = Hp.activations(B * S, 2 * C, seed=31).view(B, S, 2 * C).to(cuda_device)
+    wk = (1.0 + 0.1 * torch.randn(C, generator=Hp.gen(2))).to(cuda_device)
+    scale = 0.125 * math.sqrt(0.125)
+    k8, v8 = nat.kv_prep(kv[..., :C], kv[..., C:], wk, H, True, scale)
+    assert torch.equal(Hp.bits(k8), Hp.bits(nat.qk_norm_rope_prep(kv[..., :C], wk, None, H, True, scale)))
+    want_v = kv[..., C:].view(B, S, H, 64).transpose(1, 2).to(E4M3)
+    assert torch.equal(Hp.bits(v8), Hp.bits(want_v.contiguous()))
+
+
+@pytest.mark.parametrize("B,S", [(2, 70), (1, 128), (3, 33)])
+def test_qk_prep_without_rotation_two_rows_per_cta(nat, cuda_device, B, S):
+    """Without rotary tables an even number of rows runs two rows per CTA (B=3, S=33 is odd and takes the
+    one-row kernel): both against the separate ops (RMS norm, per-head Hadamard + cast)."""
+    H = 32
+    C = H * 64
+    x = Hp.activations(B * S, C, seed=29 + S).view(B, S, C).to(cuda_device)
+    w = (1.0 + 0.1 * torch.randn(C, generator=Hp.gen(4))).to(cuda_device)
+    scale = 0.125 * math.sqrt(0.125)
+    got = nat.qk_norm_rope_prep(x, w, None, H, True, scale)
+    normed = nat.rms_norm(x, w, None)[0]
+    want = nat.fast_hadamard_transform(normed.view(B, S, H, 64).transpose(1, 2).contiguous(), scale, E4M3)
+    diff = (Hp.bits(got) != Hp.bits(want)).float().mean().item()
+    assert diff < 2e-3, diff                                   # the mean-square summation order is the only difference
+
+
 def test_head_slices_written_into_several_full_buffers(nat, cuda_device):
     """The multi-destination output used by gather-free head sharding, on one GPU: two "ranks" each own
     half of the heads and store them into both of two full token-major buffers."""
