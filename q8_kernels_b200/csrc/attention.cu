@@ -188,7 +188,7 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             ptx::mbar_init(v_full(s), 1);
         }
         ptx::mbar_init(slot_free, 1);
-        ptx::mbar_init(s_full, 1);
+        ptx::mbar_init(s_full, 2);                              // one commit from each of the two MMA-issuing threads
         ptx::mbar_init(step_end, 4);
         ptx::mbar_init(q_free(0), 1);
         ptx::mbar_init(q_free(1), 1);
@@ -258,8 +258,15 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     while (ptx::globaltimer_ns() - t0 < 50000ull) {}
                 }
             }
-        } else if (warp == 1) {
-            // -------------------------------------------- MMA issuer
+        } else if (warp == 1 || warp == 2) {
+            // -------------------------------------------- MMA issuers: warp 1 issues O += P.V, warp 2 issues S = Q.K^T.
+            // The two chains touch different accumulators and operands, and each issue costs the issuing thread
+            // several hundred clocks (wait, descriptors, two MMAs, commit); side by side, the scores of block
+            // i+2 are on their way half as long after step i ends as when one thread issued both.
+            // s_full takes one commit from each thread per phase.  Phases of one tile: 0 = Q.K^T(0); 1 = Q.K^T(1)
+            // (if any); i+2 = P.V(i) and Q.K^T(i+2) (if any).  So phase i+1, which the softmax warps wait for in
+            // the middle of step i, says that the scores of block i+1 are in TMEM AND (i >= 1) that O holds P.V
+            // up to block i-1; phase nblk+1 says that O is complete.
             if (lane == 0) {
                 constexpr uint32_t IDESC = ptx::make_idesc_e4m3(kAttnBM, kAttnBN);
                 // P.V with V as rows: B operand MN-major (bit 16); its 32-key K slices are 32 rows of 64 bytes apart
@@ -267,46 +274,55 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 constexpr uint32_t V_KSTEP = V_ROWS ? (32 * 64) >> 4 : 2;
                 const uint32_t s_tmem = tmem_base;
                 const uint32_t o_tmem = tmem_base + kAttnOCol;
-                // s_full phases of one tile: 0 = Q.K^T(0); 1 = Q.K^T(1) (if any); i+2 = P.V(i) and Q.K^T(i+2)
-                // (if any).  So phase i+1, which the softmax warps wait for in the middle of step i, says that
-                // the scores of block i+1 are in TMEM AND (i >= 1) that O holds P.V up to block i-1; phase
-                // nblk+1 says that O is complete.
+                const bool pv_thread = warp == 1;
                 for (int t = 0; t < n_tiles; ++t) {
                     const uint32_t e_base = MULTI ? (uint32_t)t * (uint32_t)(nblk + 2) : 0u;   // step_end phases of earlier tiles
                     // The softmax warps must have seen the last s_full phase of the tile before (they then
                     // arrive once more) before this tile completes another one.
                     if (MULTI && t > 0) bounded_wait(step_end, (e_base - 1u) & 1u, abort_addr, 5);
-                    const uint64_t q_desc = ptx::make_kmajor_desc(smem_base + q_off(t & 1), 64);
-                    auto issue_qk = [&](int j) {
-                        const int s = j % kAttnKS;
-                        bounded_wait(k_full(s), (uint32_t)(j / kAttnKS) & 1u, abort_addr, 5);
-                        ptx::tcgen05_fence_after_sync();
-                        const uint64_t k_desc = ptx::make_kmajor_desc(smem_base + L::kKOff + s * L::kKBytes, 64);
-#pragma unroll
-                        for (int k = 0; k < kAttnD / 32; ++k)
-                            ptx::mma_f8f6f4(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC, k > 0 ? 1u : 0u);
-                    };
-                    bounded_wait(q_full(t & 1), (uint32_t)(t >> 1) & 1u, abort_addr, 5);
-                    issue_qk(0);                                 // (the score tile is free: S(last) of the tile before
-                    ptx::tcgen05_commit(s_full);                 //  went to registers before its last step ended)
-                    bounded_wait(step_end, e_base & 1u, abort_addr, 5);          // S(0) is in registers
-                    if (nblk > 1) issue_qk(1);
-                    ptx::tcgen05_commit(s_full);
-                    for (int i = 0; i < nblk; ++i) {
-                        const int s = i % kAttnKS;
-                        bounded_wait(step_end, (e_base + (uint32_t)i + 1u) & 1u, abort_addr, 5);   // P(i) written, O rescaled, S free
-                        bounded_wait(v_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_addr, 5);
-                        ptx::tcgen05_fence_after_sync();
-                        const uint64_t p_desc = ptx::make_kmajor_desc(smem_base + L::kPOff + (i & 1) * L::kPBytes, 64);
-                        const uint64_t v_desc = ptx::make_kmajor_desc(smem_base + L::kVOff + s * L::kVBytes, 64);
-#pragma unroll
-                        for (int k = 0; k < kAttnBN / 32; ++k)
-                            ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + V_KSTEP * k, IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
-                        if (i + 2 < nblk) issue_qk(i + 2);
+                    if (pv_thread) {
+                        ptx::tcgen05_commit(s_full);             // phases 0 and 1 carry no P.V: this thread's share is empty
+                        bounded_wait(step_end, e_base & 1u, abort_addr, 5);
                         ptx::tcgen05_commit(s_full);
-                        ptx::tcgen05_commit(slot_free);
+                        for (int i = 0; i < nblk; ++i) {
+                            const int s = i % kAttnKS;
+                            bounded_wait(step_end, (e_base + (uint32_t)i + 1u) & 1u, abort_addr, 5);   // P(i) written, O rescaled
+                            bounded_wait(v_full(s), (uint32_t)(i / kAttnKS) & 1u, abort_addr, 5);
+                            ptx::tcgen05_fence_after_sync();
+                            const uint64_t p_desc = ptx::make_kmajor_desc(smem_base + L::kPOff + (i & 1) * L::kPBytes, 64);
+                            const uint64_t v_desc = ptx::make_kmajor_desc(smem_base + L::kVOff + s * L::kVBytes, 64);
+#pragma unroll
+                            for (int k = 0; k < kAttnBN / 32; ++k)
+                                ptx::mma_f8f6f4(o_tmem, p_desc + 2 * k, v_desc + V_KSTEP * k, IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
+                            ptx::tcgen05_commit(s_full);
+                            // K(i) was read by Q.K^T(i), whose scores the softmax warps have long consumed
+                            ptx::tcgen05_commit(slot_free);
+                        }
+                        // (the last Q.K^T of the tile retired before the softmax warps could finish its block)
+                        if (MULTI) ptx::tcgen05_commit(q_free(t & 1));
+                    } else {
+                        const uint64_t q_desc = ptx::make_kmajor_desc(smem_base + q_off(t & 1), 64);
+                        auto issue_qk = [&](int j) {
+                            const int s = j % kAttnKS;
+                            bounded_wait(k_full(s), (uint32_t)(j / kAttnKS) & 1u, abort_addr, 5);
+                            ptx::tcgen05_fence_after_sync();
+                            const uint64_t k_desc = ptx::make_kmajor_desc(smem_base + L::kKOff + s * L::kKBytes, 64);
+#pragma unroll
+                            for (int k = 0; k < kAttnD / 32; ++k)
+                                ptx::mma_f8f6f4(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC, k > 0 ? 1u : 0u);
+                        };
+                        bounded_wait(q_full(t & 1), (uint32_t)(t >> 1) & 1u, abort_addr, 5);
+                        issue_qk(0);                             // (the score tile is free: S(last) of the tile before
+                        ptx::tcgen05_commit(s_full);             //  went to registers before its last step ended)
+                        bounded_wait(step_end, e_base & 1u, abort_addr, 5);      // S(0) is in registers
+                        if (nblk > 1) issue_qk(1);
+                        ptx::tcgen05_commit(s_full);
+                        for (int i = 0; i < nblk; ++i) {
+                            bounded_wait(step_end, (e_base + (uint32_t)i + 1u) & 1u, abort_addr, 5);   // S(i+1) is in registers
+                            if (i + 2 < nblk) issue_qk(i + 2);
+                            ptx::tcgen05_commit(s_full);
+                        }
                     }
-                    if (MULTI) ptx::tcgen05_commit(q_free(t & 1));
                 }
             }
         }
