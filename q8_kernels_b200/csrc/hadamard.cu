@@ -391,22 +391,23 @@ hadamard_row_kernel(const Tin* __restrict__ x, Tout* __restrict__ out, float* __
 #pragma unroll
         for (int k = 0; k < ITEMS; ++k) {
             if (FULL || t * V + k * 8 < dim) {
-                float s8[8], h8[8];
-                load_vec<__nv_bfloat16, 8>(sc + k * 8, s8);
-                load_vec<__nv_bfloat16, 8>(sh + k * 8, h8);
+                // packed bf16 arithmetic gives exactly the roundings of the separate ops: a product of two
+                // bf16 values is exact in fp32, and a sum of two is either exact in fp32 or so lopsided that
+                // both roundings return the larger operand; _rn keeps multiply and add from fusing
+                const uint4 s8 = *reinterpret_cast<const uint4*>(sc + k * 8);
+                const uint4 h8 = *reinterpret_cast<const uint4*>(sh + k * 8);
+                const __nv_bfloat162 one2 = __floats2bfloat162_rn(1.0f, 1.0f);
 #pragma unroll
                 for (int j = 0; j < 8; j += 2) {
-                    using BF = __nv_bfloat16;
+                    const uint32_t sw = j == 0 ? s8.x : (j == 2 ? s8.y : (j == 4 ? s8.z : s8.w));
+                    const uint32_t hw = j == 0 ? h8.x : (j == 2 ? h8.y : (j == 4 ? h8.z : h8.w));
                     const float2 xr2 = fmul2(make_float2(v[k * 8 + j], v[k * 8 + j + 1]), make_float2(rr, rr));
-                    const float2 n = round_through2<BF>(xr2.x, xr2.y);
-                    const float2 s1 = fadd2(make_float2(1.0f, 1.0f), make_float2(s8[j], s8[j + 1]));
-                    const float2 m1 = round_through2<BF>(s1.x, s1.y);
-                    const float2 nm = fmul2(n, m1);
-                    const float2 tm = round_through2<BF>(nm.x, nm.y);
-                    const float2 th = fadd2(tm, make_float2(h8[j], h8[j + 1]));
-                    const float2 u = round_through2<BF>(th.x, th.y);
-                    v[k * 8 + j] = u.x;
-                    v[k * 8 + j + 1] = u.y;
+                    const __nv_bfloat162 n = __floats2bfloat162_rn(xr2.x, xr2.y);
+                    const __nv_bfloat162 m1 = __hadd2_rn(one2, *reinterpret_cast<const __nv_bfloat162*>(&sw));
+                    const __nv_bfloat162 u = __hadd2_rn(__hmul2_rn(n, m1), *reinterpret_cast<const __nv_bfloat162*>(&hw));
+                    const uint32_t uw = *reinterpret_cast<const uint32_t*>(&u);
+                    v[k * 8 + j] = __uint_as_float(uw << 16);
+                    v[k * 8 + j + 1] = __uint_as_float(uw & 0xffff0000u);
                 }
             }
         }
