@@ -177,22 +177,50 @@ rope_kernel(const Tin* __restrict__ x, const float* __restrict__ cosf_, const fl
     store_vec<Tout, kItem>(out + row * (int64_t)dim + e, o);
 }
 
-// fma_kernel (csrc/ops/fma_cuda.cu:92-95).
+// fma_kernel (csrc/ops/fma_cuda.cu:92-95).  16 elements per thread (one 16-byte load of x and one store),
+// e4m3 -> fp32 through the packed e4m3x2 -> f16x2 conversion, the c10 cast eight values at a time.
+__device__ __forceinline__ void e4m3x4_to_float(uint32_t w, float (&o)[4]) {
+    const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xffffu), __NV_E4M3);
+    const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w >> 16), __NV_E4M3);
+    const float2 a = __half22float2(__half2(lo)), c = __half22float2(__half2(hi));
+    o[0] = a.x; o[1] = a.y; o[2] = c.x; o[3] = c.y;
+}
 template <typename Ty, typename Tz, int T>
 __global__ void __launch_bounds__(T)
 fma_kernel(const e4m3_t* __restrict__ x, const Ty* __restrict__ y, const Tz* __restrict__ z,
-           e4m3_t* __restrict__ out, int dim, int64_t y_every, int64_t z_every, float scale_add) {
-    const int64_t row = blockIdx.x;
-    const int e = (blockIdx.y * T + threadIdx.x) * kItem;
+           e4m3_t* __restrict__ out, int dim, unsigned y_every, unsigned z_every, float scale_add) {
+    constexpr int E = 16;
+    const unsigned row = blockIdx.x;                           // < 2^31 rows (checked by the caller)
+    const int e = (blockIdx.y * T + threadIdx.x) * E;
     if (e >= dim) return;
-    float xv[kItem], yv[kItem], zv[kItem], o[kItem];
-    load_vec<e4m3_t, kItem>(x + row * (int64_t)dim + e, xv);
-    load_vec<Ty, kItem>(y + (row / y_every) * (int64_t)dim + e, yv);
-    load_vec<Tz, kItem>(z + (row / z_every) * (int64_t)dim + e, zv);
+    const uint4 xw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(x) + (int64_t)row * dim + e);
+    float xv[E], yv[E], zv[E];
+    {
+        float t4[4];
+        e4m3x4_to_float(xw.x, t4); xv[0] = t4[0]; xv[1] = t4[1]; xv[2] = t4[2]; xv[3] = t4[3];
+        e4m3x4_to_float(xw.y, t4); xv[4] = t4[0]; xv[5] = t4[1]; xv[6] = t4[2]; xv[7] = t4[3];
+        e4m3x4_to_float(xw.z, t4); xv[8] = t4[0]; xv[9] = t4[1]; xv[10] = t4[2]; xv[11] = t4[3];
+        e4m3x4_to_float(xw.w, t4); xv[12] = t4[0]; xv[13] = t4[1]; xv[14] = t4[2]; xv[15] = t4[3];
+    }
+    load_vec<Ty, E>(y + (int64_t)(row / y_every) * dim + e, yv);
+    load_vec<Tz, E>(z + (int64_t)(row / z_every) * dim + e, zv);
+    uint4 ow;
 #pragma unroll
-    for (int j = 0; j < kItem; ++j)
-        o[j] = __fadd_rn(__fmul_rn(xv[j], __fadd_rn(yv[j], scale_add)), zv[j]);
-    store_vec<e4m3_t, kItem>(out + row * (int64_t)dim + e, o);
+    for (int h = 0; h < 2; ++h) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {                       // packed fp32x2: each lane rounds like the scalar form
+            const int i = h * 8 + j;
+            const float2 r = fadd2(fmul2(make_float2(xv[i], xv[i + 1]),
+                                         fadd2(make_float2(yv[i], yv[i + 1]), make_float2(scale_add, scale_add))),
+                                   make_float2(zv[i], zv[i + 1]));
+            o[j] = r.x;
+            o[j + 1] = r.y;
+        }
+        const uint2 w = pack8_e4m3_c10(o);
+        if (h == 0) { ow.x = w.x; ow.y = w.y; } else { ow.z = w.x; ow.w = w.y; }
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(out) + (int64_t)row * dim + e) = ow;
 }
 
 // gelu_forward_kernel (csrc/ops/gelu_forward_cuda.cu:12-16).
@@ -446,8 +474,9 @@ extern "C" int q8k_fma_8bit(const void* x, const void* y, int y_dtype, const voi
     Q8K_REQUIRE(y_every >= 1 && z_every >= 1, Q8K_ERR_INVALID_ARG, "fma_8bit: broadcast periods must be >= 1");
     cudaStream_t st = (cudaStream_t)stream;
     constexpr int T = 128;
-    dim3 grid((unsigned)rows, (unsigned)((dim / kItem + T - 1) / T));
-#define Q8K_FMA(TY, TZ) fma_kernel<TY, TZ, T><<<grid, T, 0, st>>>((const e4m3_t*)x, (const TY*)y, (const TZ*)z, (e4m3_t*)out, dim, y_every, z_every, scale_add)
+    dim3 grid((unsigned)rows, (unsigned)((dim / 16 + T - 1) / T));
+    const unsigned ye = (unsigned)(y_every > rows ? rows : y_every), ze = (unsigned)(z_every > rows ? rows : z_every);
+#define Q8K_FMA(TY, TZ) fma_kernel<TY, TZ, T><<<grid, T, 0, st>>>((const e4m3_t*)x, (const TY*)y, (const TZ*)z, (e4m3_t*)out, dim, ye, ze, scale_add)
     if (y_dtype == Q8K_DT_F32 && z_dtype == Q8K_DT_F32) Q8K_FMA(float, float);
     else if (y_dtype == Q8K_DT_F32 && z_dtype == Q8K_DT_E4M3) Q8K_FMA(float, e4m3_t);
     else if (y_dtype == Q8K_DT_BF16 && z_dtype == Q8K_DT_BF16) Q8K_FMA(__nv_bfloat16, __nv_bfloat16);
