@@ -190,6 +190,35 @@ def test_paired_qk_prep_is_two_single_calls(nat, cuda_device):
     assert torch.equal(Hp.bits(k8), Hp.bits(nat.qk_norm_rope_prep(qkv[..., C:2 * C], wk, fc, H, True, scale)))
 
 
+@pytest.mark.parametrize("B,H,M,N,lens,out", [(2, 32, 900, 128, [77, 128], torch.bfloat16),
+                                              (2, 32, 900, 192, None, torch.bfloat16),
+                                              (3, 24, 1100, 100, [0, 100, 33], None),
+                                              (1, 64, 1536, 64, None, None)])
+def test_short_key_sequences_with_several_query_tiles_per_cta(nat, cuda_device, B, H, M, N, lens, out):
+    """With at most three key blocks and more (batch, head) pairs than a third of the device's CTA slots, a CTA
+    keeps K/V and walks over several query tiles, unevenly distributed here (7, 8, 9 or 12 tiles over fewer
+    CTAs, the last tile partial); every output row against the oracle, e4m3 and bf16 outputs, V both ways."""
+    d = cuda_device
+    q8, k8, vt, ks = _fp8_operands(B, H, M, N, seed=M + N + H)
+    mask = None if lens is None else torch.tensor(lens, dtype=torch.int32)
+    ref = O.flash_attention(q8, k8, vt, ks, mask, torch.bfloat16)
+    md = None if mask is None else mask.to(d)
+    got = nat.flash_attention(q8.to(d), k8.to(d), vt.to(d), ks, md, out)
+    if out is None:
+        assert got.dtype == E4M3
+        ref8 = O.flash_attention(q8, k8, vt, ks, mask, E4M3)
+        per_batch = [(Hp.bits(got[b].cpu()) != Hp.bits(ref8[b])).float().mean().item() for b in range(B)]
+        assert max(per_batch) < 0.02, per_batch
+    else:
+        err = Hp.rel_fro(got.float(), ref.float())
+        assert err <= TOL, f"rel fro {err:.3e}"
+    v_rows = vt[..., :N].transpose(2, 3).contiguous()
+    again = nat.flash_attention(q8.to(d), k8.to(d), v_rows.to(d), ks, md, out, v_rows=True)
+    assert torch.equal(Hp.bits(again), Hp.bits(got))
+    tm = nat.flash_attention(q8.to(d), k8.to(d), vt.to(d), ks, md, out, token_major_out=True)      # stored [B,M,H,64]
+    assert torch.equal(Hp.bits(tm.contiguous()), Hp.bits(got))
+
+
 def test_qkv_prep_adds_the_plain_cast_of_v(nat, cuda_device):
     """The three slices of a fused QKV projection in one launch: Q and K as in the paired call, V the
     unscaled e4m3 cast as rows [B,H,S,64]."""
