@@ -346,7 +346,10 @@ static int gemm_8bit(bool int8, const void* a, const void* b, const float* bias,
                 "%s: batch * rows exceeds 2^31", op);
     if (M == 0) return Q8K_OK;
 
-    const bool bn256 = N > 128;
+    // 256-column tiles unless they would leave most of the device idle (e.g. the 128-token K/V projection
+    // of a cross-attention): then twice as many 128-column tiles, each streaming half as much of B
+    const int64_t tiles256 = (int64_t)((M + kGemmBM - 1) / kGemmBM) * ((N + 255) / 256) * batch;
+    const bool bn256 = N > 128 && tiles256 >= gemm_num_sms() / 2;
     const int bn = bn256 ? 256 : 128;
 
     CUtensorMap ta, tb;
