@@ -17,21 +17,26 @@
 // Structure: one CTA per 128 query rows of one (batch, head), two warpgroups
 // whose register budgets are rebalanced with setmaxnreg (24 / 136 per thread),
 // three CTAs per SM (registers; 3 x 128 TMEM columns).
-//   warp 0      TMA: Q tile once, then K (64 keys x 64 B) and V^T (64 x 64 keys)
-//               tiles, all 64B-swizzled, into rings of three; one wait per block
-//   warp 1      TMEM allocation; one thread issues S = Q.K^T (2 x tcgen05.mma
-//               M128 N64 K32) into TMEM columns [0,64) and O += P.V (2 x M128 N64
-//               K32) into columns [64,128); one blocking wait per block
+//   warp 0      TMA: Q tile once, then K (64 keys x 64 B) and V (as 64 x 64 rows, or V^T as the
+//               reference lays it out) tiles, all 64B-swizzled, into rings of three; one wait per block
+//   warp 1      TMEM allocation; one thread issues O += P.V (2 x tcgen05.mma M128 N64 K32) into TMEM
+//               columns [64,128)
+//   warp 2      one thread issues S = Q.K^T (2 x M128 N64 K32) into columns [0,64); the two issuing
+//               threads run side by side, one blocking wait per block each
 //   warps 4-7   softmax, one thread per query row: the scores of block i sit in
 //               registers (each half is refilled from TMEM with block i+1 as soon
 //               as its exps are done), max, exp2, P as e4m3 into one of two
 //               swizzled shared tiles (the A operand of P.V), then -- only when a
 //               row max of the warp moved -- O *= alpha in TMEM through the
-//               registers of the finished half; at the end O / l -> global
-// Three mbarriers carry the steady state: step_end (softmax -> MMA: P written, O
-// rescaled, S read), s_full (MMA -> softmax: next scores landed AND the previous
-// P.V retired) and slot_free (MMA -> TMA).  Every wait is on consecutive phases
-// of its barrier, so a parity is never ambiguous, and every wait is bounded.
+//               registers of the finished half; at the end O / l is parked in the warp's own
+//               P rows and leaves through TMA stores (whole-row plain stores for several outputs)
+// Three mbarriers carry the steady state: step_end (softmax -> MMA threads: P written, O
+// rescaled, S read), s_full (one commit from each MMA thread -> softmax: next scores landed AND the
+// previous P.V retired) and slot_free (MMA -> TMA).  Every wait is on consecutive phases
+// of its barrier, no barrier can complete a second phase before its waiters have seen the first,
+// so a parity is never ambiguous; and every wait is bounded.
+// With at most three key blocks (cross-attention) a CTA keeps K/V and walks over several query
+// tiles: see the MULTI template parameter.
 
 #include <type_traits>
 
