@@ -188,39 +188,61 @@ __device__ __forceinline__ void e4m3x4_to_float(uint32_t w, float (&o)[4]) {
 template <typename Ty, typename Tz, int T>
 __global__ void __launch_bounds__(T)
 fma_kernel(const e4m3_t* __restrict__ x, const Ty* __restrict__ y, const Tz* __restrict__ z,
-           e4m3_t* __restrict__ out, int dim, unsigned y_every, unsigned z_every, float scale_add) {
-    constexpr int E = 16;
-    const unsigned row = blockIdx.x;                           // < 2^31 rows (checked by the caller)
+           e4m3_t* __restrict__ out, unsigned rows, int dim, unsigned y_every, unsigned z_every, float scale_add) {
+    constexpr int E = 16;                                      // columns per thread
+    constexpr int R = 4;                                       // rows per thread: y and z are widened once for all of them
+    const unsigned row0 = blockIdx.x * R;                      // < 2^31 rows (checked by the caller)
     const int e = (blockIdx.y * T + threadIdx.x) * E;
     if (e >= dim) return;
-    const uint4 xw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(x) + (int64_t)row * dim + e);
-    float xv[E], yv[E], zv[E];
-    {
-        float t4[4];
-        e4m3x4_to_float(xw.x, t4); xv[0] = t4[0]; xv[1] = t4[1]; xv[2] = t4[2]; xv[3] = t4[3];
-        e4m3x4_to_float(xw.y, t4); xv[4] = t4[0]; xv[5] = t4[1]; xv[6] = t4[2]; xv[7] = t4[3];
-        e4m3x4_to_float(xw.z, t4); xv[8] = t4[0]; xv[9] = t4[1]; xv[10] = t4[2]; xv[11] = t4[3];
-        e4m3x4_to_float(xw.w, t4); xv[12] = t4[0]; xv[13] = t4[1]; xv[14] = t4[2]; xv[15] = t4[3];
+    const unsigned nr = rows - row0 < (unsigned)R ? rows - row0 : (unsigned)R;
+    // the common case: the rows of this thread share one y row and one z row (modulation rows broadcast over tokens)
+    const bool shared_yz = row0 / y_every == (row0 + nr - 1) / y_every && row0 / z_every == (row0 + nr - 1) / z_every;
+    float yv[E], zv[E];
+    if (shared_yz) {
+        load_vec<Ty, E>(y + (int64_t)(row0 / y_every) * dim + e, yv);
+        load_vec<Tz, E>(z + (int64_t)(row0 / z_every) * dim + e, zv);
+#pragma unroll
+        for (int j = 0; j < E; ++j) yv[j] = __fadd_rn(yv[j], scale_add);
     }
-    load_vec<Ty, E>(y + (int64_t)(row / y_every) * dim + e, yv);
-    load_vec<Tz, E>(z + (int64_t)(row / z_every) * dim + e, zv);
-    uint4 ow;
+    uint4 xw[R];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        float o[8];
+    for (int r = 0; r < R; ++r)
+        if ((unsigned)r < nr) xw[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(x) + (int64_t)(row0 + r) * dim + e);
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {                       // packed fp32x2: each lane rounds like the scalar form
-            const int i = h * 8 + j;
-            const float2 r = fadd2(fmul2(make_float2(xv[i], xv[i + 1]),
-                                         fadd2(make_float2(yv[i], yv[i + 1]), make_float2(scale_add, scale_add))),
-                                   make_float2(zv[i], zv[i + 1]));
-            o[j] = r.x;
-            o[j + 1] = r.y;
+    for (int r = 0; r < R; ++r) {
+        if ((unsigned)r >= nr) break;
+        const unsigned row = row0 + r;
+        if (!shared_yz) {
+            load_vec<Ty, E>(y + (int64_t)(row / y_every) * dim + e, yv);
+            load_vec<Tz, E>(z + (int64_t)(row / z_every) * dim + e, zv);
+#pragma unroll
+            for (int j = 0; j < E; ++j) yv[j] = __fadd_rn(yv[j], scale_add);
         }
-        const uint2 w = pack8_e4m3_c10(o);
-        if (h == 0) { ow.x = w.x; ow.y = w.y; } else { ow.z = w.x; ow.w = w.y; }
+        float xv[E];
+        {
+            float t4[4];
+            e4m3x4_to_float(xw[r].x, t4); xv[0] = t4[0]; xv[1] = t4[1]; xv[2] = t4[2]; xv[3] = t4[3];
+            e4m3x4_to_float(xw[r].y, t4); xv[4] = t4[0]; xv[5] = t4[1]; xv[6] = t4[2]; xv[7] = t4[3];
+            e4m3x4_to_float(xw[r].z, t4); xv[8] = t4[0]; xv[9] = t4[1]; xv[10] = t4[2]; xv[11] = t4[3];
+            e4m3x4_to_float(xw[r].w, t4); xv[12] = t4[0]; xv[13] = t4[1]; xv[14] = t4[2]; xv[15] = t4[3];
+        }
+        uint4 ow;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {                   // packed fp32x2: each lane rounds like the scalar form
+                const int i = h * 8 + j;
+                const float2 v2 = fadd2(fmul2(make_float2(xv[i], xv[i + 1]), make_float2(yv[i], yv[i + 1])),
+                                        make_float2(zv[i], zv[i + 1]));
+                o[j] = v2.x;
+                o[j + 1] = v2.y;
+            }
+            const uint2 w = pack8_e4m3_c10(o);
+            if (h == 0) { ow.x = w.x; ow.y = w.y; } else { ow.z = w.x; ow.w = w.y; }
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(out) + (int64_t)row * dim + e) = ow;
     }
-    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(out) + (int64_t)row * dim + e) = ow;
 }
 
 // gelu_forward_kernel (csrc/ops/gelu_forward_cuda.cu:12-16).
@@ -474,9 +496,9 @@ extern "C" int q8k_fma_8bit(const void* x, const void* y, int y_dtype, const voi
     Q8K_REQUIRE(y_every >= 1 && z_every >= 1, Q8K_ERR_INVALID_ARG, "fma_8bit: broadcast periods must be >= 1");
     cudaStream_t st = (cudaStream_t)stream;
     constexpr int T = 128;
-    dim3 grid((unsigned)rows, (unsigned)((dim / 16 + T - 1) / T));
+    dim3 grid((unsigned)((rows + 3) / 4), (unsigned)((dim / 16 + T - 1) / T));
     const unsigned ye = (unsigned)(y_every > rows ? rows : y_every), ze = (unsigned)(z_every > rows ? rows : z_every);
-#define Q8K_FMA(TY, TZ) fma_kernel<TY, TZ, T><<<grid, T, 0, st>>>((const e4m3_t*)x, (const TY*)y, (const TZ*)z, (e4m3_t*)out, dim, ye, ze, scale_add)
+#define Q8K_FMA(TY, TZ) fma_kernel<TY, TZ, T><<<grid, T, 0, st>>>((const e4m3_t*)x, (const TY*)y, (const TZ*)z, (e4m3_t*)out, (unsigned)rows, dim, ye, ze, scale_add)
     if (y_dtype == Q8K_DT_F32 && z_dtype == Q8K_DT_F32) Q8K_FMA(float, float);
     else if (y_dtype == Q8K_DT_F32 && z_dtype == Q8K_DT_E4M3) Q8K_FMA(float, e4m3_t);
     else if (y_dtype == Q8K_DT_BF16 && z_dtype == Q8K_DT_BF16) Q8K_FMA(__nv_bfloat16, __nv_bfloat16);

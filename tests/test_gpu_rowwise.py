@@ -152,11 +152,14 @@ def test_rope_bit_exact_and_reference_vectors(nat, cuda_device):
 
 @pytest.mark.parametrize("ydt,zdt", [(torch.float32, torch.float32), (torch.float32, E4M3),
                                      (torch.bfloat16, torch.bfloat16)])
-def test_fma_bit_exact(nat, cuda_device, ydt, zdt):
+@pytest.mark.parametrize("S,z_rows", [(12, 12), (13, 1), (8, 1), (13, 13)])
+def test_fma_bit_exact(nat, cuda_device, ydt, zdt, S, z_rows):
+    """z per token or broadcast like y; S = 13 makes row groups of four straddle the two batch entries and
+    leaves a partial last group (the kernel widens y and z once per group when the group shares them)."""
     g = Hp.gen(10)
-    x = O.c10_e4m3(torch.randn(2, 12, 2048, generator=g))
+    x = O.c10_e4m3(torch.randn(2, S, 2048, generator=g))
     y = (torch.randn(2, 1, 2048, generator=g) * 0.3)
-    z = torch.randn(2, 12, 2048, generator=g)
+    z = torch.randn(2, z_rows, 2048, generator=g)
     y = y.to(ydt)
     z = O.c10_e4m3(z) if zdt == E4M3 else z.to(zdt)
     ref = O.fma_8bit(x, y, z, 1.0)
