@@ -191,7 +191,7 @@ def test_norm_modulate_quant_matches_unfused_chain(q8, cuda_device):
 
 @pytest.mark.parametrize("kind", ["int8", "fp8"])
 @pytest.mark.parametrize("with_gate", [True, False])
-@pytest.mark.parametrize("M,N,K", [(200, 512, 256), (384, 2048, 2048), (96, 128, 128)])
+@pytest.mark.parametrize("M,N,K", [(200, 512, 256), (384, 2048, 2048), (96, 128, 128), (300, 272, 192), (515, 1040, 320)])
 def test_mm_gate_residual_is_bit_identical_to_separate_ops(q8, cuda_device, kind, with_gate, M, N, K):
     qd = torch.int8 if kind == "int8" else E4M3
     d = cuda_device
