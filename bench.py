@@ -522,6 +522,23 @@ def detail_dit(q8, dev, rank, world):
                            "all_gather_into_tensor of the final [1,6144,2048] bf16 hidden states inside the timed region")
     del stack
     torch.cuda.empty_cache()
+    # the same block built from FP8 linears (per-token e4m3 activations, e4m3 weights), one block only
+    ms_fp8 = float("nan")
+    try:
+        cfg8 = q8.blocks.LTXStackConfig(num_layers=1, linear="fp8")
+        stack8 = q8.blocks.random_init_(q8.blocks.LTXStack(cfg8), seed=11, device=dev)
+        with torch.no_grad():
+            tproj8 = stack8.caption_projection(text)
+            blk8 = stack8.transformer_blocks[0]
+            ms_fp8 = timed(lambda: blk8(x, freqs, None, tproj8, lens, ts), 10)
+        del stack8, blk8
+    except Exception as exc:                                   # noqa: BLE001  (an extra figure: report, do not fail the bench)
+        out["block_fp8_linears_unavailable"] = f"{type(exc).__name__}: {str(exc)[:120]}"
+    ms_fp8 = reduce_max(ms_fp8)
+    if ms_fp8 == ms_fp8:
+        out["block_ms_fp8_linears"] = round(ms_fp8, 4)
+    q8._lib.check_status(dev)
+    torch.cuda.empty_cache()
     return out
 
 
