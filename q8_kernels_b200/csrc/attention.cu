@@ -493,12 +493,14 @@ flash_attn_fp8_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             // the warp writes the 32 rows out with 8 (bf16) or 4 (e4m3) lanes per row.
             const float inv = (l_run == 0.f || l_run != l_run) ? 1.f : 1.f / l_run;
             const uint32_t stage = smem_base + L::kPOff + (uint32_t)(quarter * 32) * kAttnBN;   // + kPBytes: second half
-#pragma unroll 1
+            // both halves of the O row come in at once, into the registers the scores lived in
+            __syncwarp();
+            ptx::tmem_ld_32x32b_x32(t_lane + kAttnOCol, cur[0]);
+            ptx::tmem_ld_32x32b_x32(t_lane + kAttnOCol + 32, cur[1]);
+            ptx::tmem_wait_ld();
+#pragma unroll
             for (int h = 0; h < kAttnD / 32; ++h) {
-                uint32_t orow[32];
-                __syncwarp();
-                ptx::tmem_ld_32x32b_x32(t_lane + kAttnOCol + h * 32, orow);
-                ptx::tmem_wait_ld();
+                const uint32_t (&orow)[32] = cur[h];
                 const uint32_t half = stage + (uint32_t)h * L::kPBytes;
                 if (p.out_e4m3) {                                // 32 bytes per row and half: 2 pieces, swizzled by row bit 2
 #pragma unroll
