@@ -104,10 +104,12 @@ template <int N> __device__ __forceinline__ void reg_alloc() {
 // 2^x for two finite x <= 0 on the FMA pipe instead of the 16-lane exp2 unit, which is the busiest unit of this
 // kernel: x is rounded to the nearest integer with the 1.5 * 2^23 trick, a quartic in the remainder f in [-0.5, 0.5]
 // follows (max relative error 2.7e-6, far below half a step of the e4m3 rounding P goes through), and the integer is
-// added into the exponent field.  x below -126 comes out as zero or a denormal (the clamp at 0 keeps the sign bit
-// clear), like ex2.approx.ftz.  The softmax step takes this path for one score in eight: more of them cost more
-// issue slots than the exp2 unit gives back (measured: 1/8 -> -1.8 %, 1/4 -> -0.5 %, 1/2 -> +8 %).
+// added into the exponent field.  x is clamped at -126 first (any finite or infinite input is safe).  The softmax
+// step takes this path for one score in eight: more of them cost more issue slots than the exp2 unit gives back
+// (measured: 1/8 -> -1.8 %, 1/4 -> -0.5 %, 1/2 -> +8 %).
 __device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    // below -126 the result is 2^-126 (as good as the zero ex2.approx.ftz returns) and the shift below cannot wrap
+    x = make_float2(fmaxf(x.x, -126.0f), fmaxf(x.y, -126.0f));
     const float2 magic = make_float2(12582912.0f, 12582912.0f);
     const float2 t = fadd2(x, magic);
     const float2 r = fadd2(t, make_float2(-12582912.0f, -12582912.0f));
@@ -117,9 +119,8 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     p = ffma2(p, f, make_float2(0.2402464896440506f, 0.2402464896440506f));
     p = ffma2(p, f, make_float2(0.6931217312812805f, 0.6931217312812805f));
     p = ffma2(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
-    const int bx = max(__float_as_int(p.x) + (__float_as_int(t.x) << 23), 0);
-    const int by = max(__float_as_int(p.y) + (__float_as_int(t.y) << 23), 0);
-    return make_float2(__int_as_float(bx), __int_as_float(by));
+    return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                       __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;

@@ -219,6 +219,25 @@ def test_short_key_sequences_with_several_query_tiles_per_cta(nat, cuda_device, 
     assert torch.equal(Hp.bits(tm.contiguous()), Hp.bits(got))
 
 
+def test_scores_far_below_the_row_maximum(nat, cuda_device):
+    """Unrotated operands with a few keys scaled up to the e4m3 range: in the blocks visited later most scores lie
+    hundreds to thousands of octaves under the running maximum, which must come out as zero weight in whatever
+    unit computes the exponential."""
+    B, H, M, N = 1, 2, 256, 512
+    g = Hp.gen(41)
+    q8 = O.c10_e4m3(torch.randn(B, H, M, 64, generator=g) * 8.0)
+    k = torch.randn(B, H, N, 64, generator=g) * 2.0
+    k[:, :, 500] *= 100.0                                      # saturates towards +-448: one dominating key in the first-visited block
+    k[:, :, 77] *= 40.0
+    k8 = O.c10_e4m3(k.clamp(-440, 440))
+    vt = O.c10_e4m3(torch.randn(B, H, 64, N, generator=g)).contiguous()
+    ref = O.flash_attention(q8, k8, vt, 1.0, None, torch.bfloat16)
+    assert torch.isfinite(ref.float()).all()
+    got = nat.flash_attention(q8.to(cuda_device), k8.to(cuda_device), vt.to(cuda_device), 1.0, None, torch.bfloat16)
+    err = Hp.rel_fro(got.float(), ref.float())
+    assert err <= TOL, f"rel fro {err:.3e}"
+
+
 def test_qkv_prep_adds_the_plain_cast_of_v(nat, cuda_device):
     """The three slices of a fused QKV projection in one launch: Q and K as in the paired call, V the
     unscaled e4m3 cast as rows [B,H,S,64]."""
