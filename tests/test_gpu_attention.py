@@ -420,3 +420,11 @@ def test_attention_cast_rows_is_the_unscaled_e4m3_cast(nat, cuda_device):
     got = nat.attention_cast_rows(v.to(cuda_device))
     assert got.shape == (2, 3, 77, 64) and got.is_contiguous()
     Hp.assert_bit_equal(got, O.c10_e4m3(v).contiguous(), "v rows")
+    # values beyond the e4m3 range, infinities and NaNs of both signs: the c10 cast gives NaN with the sign kept,
+    # where the packed hardware conversion alone would saturate (the kernel patches those groups of eight)
+    big = v.clone()
+    flat = big.reshape(-1)
+    flat[5] = 464.0; flat[6] = 465.0; flat[70] = -1000.0; flat[133] = float("inf"); flat[200] = float("-inf")
+    flat[260] = float("nan"); flat[333] = -float("nan"); flat[400] = 448.0; flat[401] = -463.9
+    got = nat.attention_cast_rows(big.to(cuda_device))
+    Hp.assert_bit_equal(got, O.c10_e4m3(big).contiguous(), "v rows with out-of-range values")

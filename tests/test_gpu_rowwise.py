@@ -165,6 +165,12 @@ def test_fma_bit_exact(nat, cuda_device, ydt, zdt, S, z_rows):
     ref = O.fma_8bit(x, y, z, 1.0)
     got = nat.fma_8bit(x.to(cuda_device), y.to(cuda_device), z.to(cuda_device), 1.0)
     Hp.assert_bit_equal(got, ref, "fma")
+    # a scale that pushes part of the results beyond 464: the c10 cast turns those into NaN, sign kept
+    y_big = (y.float() * 900.0).to(ydt)
+    ref = O.fma_8bit(x, y_big, z, 1.0)
+    assert (ref.view(torch.uint8) & 0x7F == 0x7F).any()
+    got = nat.fma_8bit(x.to(cuda_device), y_big.to(cuda_device), z.to(cuda_device), 1.0)
+    Hp.assert_bit_equal(got, ref, "fma with overflow")
 
 
 def test_gelu_forward(nat, cuda_device):
