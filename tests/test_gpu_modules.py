@@ -365,3 +365,36 @@ def test_full_stack_eager_equals_graph_replay(q8, cuda_device):
         replay2 = fn(x, grid, text, lens, ts)
     assert torch.isfinite(eager.float()).all()
     assert torch.equal(eager, replay1) and torch.equal(eager, replay2)
+
+
+def test_gate_residual_tail_over_wide_exponent_ranges(q8, cuda_device):
+    """The epilogue multiplies and adds in packed bf16; torch multiplies and adds in fp32 and rounds each result to
+    bf16.  With a zero activation the linear output is the bias, so gate, bias and residual can be given any
+    magnitudes: exponents spread over +-40 octaves, exact ties, cancellations, infinities."""
+    d = cuda_device
+    M, N, K = 256, 512, 128
+    g = Hp.gen(77)
+    aq = torch.zeros(1, M, K, dtype=torch.int8, device=d)
+    wq = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8).to(d)
+    sa = torch.ones(M, device=d)
+    sw = torch.ones(N, device=d)
+    def spread(*shape):
+        mant = 1.0 + torch.randint(0, 128, shape, generator=g).float() / 128.0
+        expo = torch.randint(-40, 41, shape, generator=g).float()
+        sign = torch.randint(0, 2, shape, generator=g).float() * 2 - 1
+        return sign * mant * torch.exp2(expo)
+    bias = spread(N).to(d)
+    gate = spread(1, 1, N).to(torch.bfloat16).to(d)
+    resid = spread(1, M, N).to(torch.bfloat16)
+    resid[0, :, 0::7] = 0.0
+    resid[0, 3, 5] = float("inf")
+    resid = resid.to(d)
+    y = q8.native.q8_mm_bias(aq, wq, bias, sa, sw, False, torch.bfloat16)
+    # make a fifth of the residuals cancel the gated value exactly or to within a few ulps
+    prod = gate * y
+    resid[0, :, 1::5] = -prod[0, :, 1::5]
+    resid[0, :, 2::5] = (-prod[0, :, 2::5].float() * (1 + 2.0 ** -7)).to(torch.bfloat16)
+    want = gate * y + resid
+    got = q8.native.mm_gate_residual(aq, wq, bias, sa, sw, gate, resid)
+    assert torch.equal(Hp.bits(got), Hp.bits(want))
+
